@@ -10,12 +10,14 @@
  *   XOTB200_LM_MIX_DELTA_RULE   generalised delta-rule recurrence with per-channel decay and removal rate;
  *                               state = one fp32 matrix per head, request and layer;
  *   XOTB200_LM_MIX_ATTENTION    grouped-query attention over a paged cache of (normed) keys and values; options: projection
- *                               biases, query/key norm, soft cap, logarithmic distance penalty, sliding window, block-local mask,
- *                               output gate per head or per entry, keys/values borrowed from an earlier layer;
+ *                               biases, query/key norm (per head or over the whole projection), soft cap, logarithmic distance
+ *                               penalty, learned bias per distance bucket, query temperature, softmax sink, sliding window,
+ *                               block-local mask, output gate per head or per entry, keys/values borrowed from an earlier layer;
  *   XOTB200_LM_MIX_GATED_DELTA  delta rule with one decay per head behind short causal convolutions;
  *                               state = fp32 matrix per head + the convolutions' last inputs.
  * A layer wraps its sublayers in grouped RMS norms before and after them, or reads the stream itself and closes with a layer norm
- * (xotb200_lm_cfg.block); its feed-forward is dense (relu^2 or xIELU) or a mixture of gated experts (xotb200_lm_layer.ff_kind).
+ * or an RMS norm (xotb200_lm_cfg.block); its feed-forward is dense (relu^2 or xIELU) or a mixture of experts (gated silu or relu^2
+ * experts, two routing rules, an optional shared expert: xotb200_lm_layer.ff_kind and the fields after it).
  * Every size and constant of a layer is a field of xotb200_lm_layer, so a model family is a table of layers, not code.
  *
  * Serving model: requests live in SLOTS (0 .. max_requests-1).  A step (xotb200_lm_step) takes a packed batch — for each
@@ -54,10 +56,21 @@ extern "C" {
 #define XOTB200_LM_FF_RELU2 0  /* W_down relu(W_up h)^2                                                                         */
 #define XOTB200_LM_FF_XIELU 1  /* W_down act(W_up h), act(z) = softplus(p) z^2 + z/2 (z > 0), (1/2 + softplus(q))(e^z - 1 - z) + z/2 (z <= 0);
                                   p, q = the two entries of l<i>.mlp.act                                                         */
-#define XOTB200_LM_FF_MOE 2    /* mixture of gated experts W_down (silu(W_gate h) * W_up h), softmax router, group-limited top-k */
+#define XOTB200_LM_FF_MOE 2    /* mixture of experts; expert form, routing rule and shared expert: expert_act, router_kind, shared_ff */
+
+#define XOTB200_LM_EXPERT_SILU_GATED 0 /* expert = W_down (silu(W_gate h) * W_up h)                                              */
+#define XOTB200_LM_EXPERT_RELU2 1      /* expert = W_down relu(W_up h)^2  (no gate matrix)                                       */
+
+#define XOTB200_LM_ROUTER_SOFTMAX_ALL 0 /* scores = softmax over all experts; group-limited top-k; weights = the chosen scores     */
+#define XOTB200_LM_ROUTER_TOPK_SOFTMAX 1 /* the `top` largest logits (W_router h + router.b) are chosen; weights = softmax over them */
 
 #define XOTB200_LM_BLOCK_GROUP_RMS 0  /* x += norm1b(mixer(norm1(x))): grouped RMS norms before and after every sublayer          */
 #define XOTB200_LM_BLOCK_POST_LN 1    /* x += LN(mixer(x)): the sublayer reads the stream itself, layer norm (weight + bias) on its output */
+#define XOTB200_LM_BLOCK_POST_RMS 2   /* x += rms(mixer(x)) * (1 + w): the same with an RMS norm whose weight is stored around zero     */
+
+#define XOTB200_LM_QKNORM_NONE 0
+#define XOTB200_LM_QKNORM_HEAD 1      /* RMS norm of every query / key head, one weight of size dim shared by the heads                 */
+#define XOTB200_LM_QKNORM_ROW 2       /* ONE RMS norm over the whole query (key) projection, weights of size heads * dim (kv_heads * dim) */
 
 #define XOTB200_LM_ROT_INTERLEAVED 0 /* pairs (2i, 2i+1)        */
 #define XOTB200_LM_ROT_HALF 1        /* pairs (i, i + dims / 2) */
@@ -81,8 +94,9 @@ typedef struct xotb200_lm_layer {
   /* -- grouped-query attention (MIX_ATTENTION) and gated delta rule (MIX_GATED_DELTA) -------------------------------------
    * MIX_ATTENTION: `heads` query heads of size `dim` share `kv_heads` key/value heads (query head a reads a / (heads / kv_heads)),
    * values of size `vdim`; the cache holds per token [keys after their norm | values].  score = q.k * scale, then
-   * softcap * tanh(score / softcap) when softcap > 0, then - r1[a] * ln(1 + r2[a] * (i - j)) when dist_bias; visible keys: j <= i,
-   * i - j < window when window > 0, floor(i / chunk) == floor(j / chunk) when chunk > 0; softmax.
+   * softcap * tanh(score / softcap) when softcap > 0, then - r1[a] * ln(1 + r2[a] * (i - j)) when dist_bias, then + rel[bucket(i - j), a]
+   * when rel_buckets > 0; visible keys: j <= i, i - j < window when window > 0, floor(i / chunk) == floor(j / chunk) when chunk > 0;
+   * softmax, whose denominator also holds exp(sink[a]) when `sink` (a term without key or value).
    * MIX_GATED_DELTA: `kv_heads` query/key heads of size `dim`, `heads` value heads of size `vdim`; q, k, v pass a causal
    * per-channel filter of `conv_taps` taps and silu; q, k unit vectors (q also / sqrt(dim)); per head S <- g S,
    * S += k (beta (v - S^T k))^T, o = S^T q with g = exp(-exp(A_log) softplus(W_a h + dt_bias)), beta = sigmoid(W_b h);
@@ -90,17 +104,30 @@ typedef struct xotb200_lm_layer {
   int32_t kv_heads;
   int32_t kv_from;    /* attention: -1 = own keys/values; else the (global) index of the earlier layer whose cache it reads */
   int32_t chunk;      /* attention: > 0 = block-local causal mask with blocks of this many positions          */
-  int32_t qk_norm;    /* attention: 1 = per-head RMS norm of queries and keys (weights q.norm / k.norm of size dim) */
+  int32_t qk_norm;    /* attention: XOTB200_LM_QKNORM_* (weights q.norm / k.norm)                              */
   int32_t proj_bias;  /* attention: 1 = q, k, v projections have biases (q.b, k.b, v.b)                       */
   int32_t dist_bias;  /* attention: 1 = logarithmic distance penalty with per-head r1, r2                     */
   int32_t conv_taps;  /* gated delta rule: taps of the short convolutions                                     */
   int32_t ff_kind;    /* XOTB200_LM_FF_*  (`ff` = inner size of the dense forms)                              */
   int32_t experts;    /* FF_MOE: number of experts, each of inner size expert_ff                              */
   int32_t expert_ff;
-  int32_t top;        /* FF_MOE: experts per token; weights = their softmax scores over ALL experts, not renormalised */
+  int32_t top;        /* FF_MOE: experts per token (their weights: router_kind)                                       */
   int32_t groups;     /* FF_MOE: experts form `groups` equal groups of neighbours (<= 1: no groups) ...        */
   int32_t groups_keep;/* ... and only experts of the groups_keep groups with the largest best score can be chosen */
   float softcap;
+  /* -- further options of MIX_ATTENTION -------------------------------------------------------------------------------- */
+  int32_t out_bias;     /* 1 = the output projection has a bias (o.b)                                            */
+  int32_t sink;         /* 1 = one learned logit per query head (sink) joins the softmax denominator            */
+  int32_t rel_buckets;  /* B > 0: learned bias rel[B, heads] per distance bucket: bucket(n) = n for n < B/2, else
+                           min(B - 1, B/2 + floor(ln(n / (B/2)) / ln(rel_max / (B/2)) * (B - B/2)))              */
+  float rel_max;        /* distance at which the last bucket is reached                                          */
+  float q_temp_coef;    /* != 0: the query at position p is multiplied by 1 + q_temp_coef * ln(floor((p + 1) / q_temp_every) + 1) */
+  int32_t q_temp_every;
+  /* -- further options of FF_MOE ---------------------------------------------------------------------------------------- */
+  int32_t expert_act;   /* XOTB200_LM_EXPERT_*                                                                   */
+  int32_t router_kind;  /* XOTB200_LM_ROUTER_*                                                                   */
+  int32_t router_bias;  /* 1 = the router logits have a bias (router.b)                                          */
+  int32_t shared_ff;    /* > 0: a shared expert of this inner size (same form as the experts) runs for every token and is added */
 } xotb200_lm_layer;
 
 typedef struct xotb200_lm_cfg {
@@ -114,6 +141,12 @@ typedef struct xotb200_lm_cfg {
   float norm_eps;
   int32_t block;         /* XOTB200_LM_BLOCK_*: how a layer wraps its sublayers; the final norm is of the same kind        */
   int32_t max_positions; /* > 0: a learned position vector pos[p] is added to the embedding; requests hold at most this many tokens */
+  int32_t pos_sinusoid;  /* 1 = a computed position vector is added to the embedding: entry 2i = sin(p f_i), 2i + 1 = cos(p f_i),
+                            f_i = sinusoid_base^(-2i / width)                                                                     */
+  float sinusoid_base;
+  int32_t embed_norm;    /* 1 = the block's closing norm (weight embed.norm) is applied to the embedding sum before the first layer */
+  float logit_scale;     /* logits are multiplied by this (0 = 1)                                                                   */
+  float logit_softcap;   /* > 0: logits <- cap * tanh(logits / cap), after the scale                                                */
 } xotb200_lm_cfg;
 
 typedef struct xotb200_lm xotb200_lm;
@@ -130,6 +163,9 @@ int xotb200_lm_destroy(xotb200_lm* e);
  * BLOCK_POST_LN models: pos, final.norm.b, l<i>.norm1 / norm1.b / norm2 / norm2.b; MIX_ATTENTION <t> in {q, q.b, q.norm, k, k.b,
  * k.norm, v, v.b, r1, r2, g, o}; MIX_GATED_DELTA <t> in {q, q.conv, k, k.conv, v, v.conv, b, a, A_log, dt_bias, norm, g, o};
  * l<i>.mlp.act (FF_XIELU); l<i>.mlp.router, l<i>.mlp.e<n>.gate / up / down (FF_MOE).
+ * BLOCK_POST_RMS models: l<i>.norm1 / norm2, embed.norm; further MIX_ATTENTION tensors: o.b, sink [heads], rel [buckets, heads]; with
+ * QKNORM_ROW q.norm / k.norm have the projection's size; further FF_MOE tensors: router.b, shared.up / shared.down; relu^2 experts
+ * have no gate matrix.
  * xotb200_lm_load_dir reads every *.safetensors of the directory (BF16 tensors) and is STRICT: a tensor of this shard that is
  * missing, has another shape or dtype, or an unknown tensor of an owned layer, is an error. */
 int xotb200_lm_load_dir(xotb200_lm* e, const char* dir);

@@ -102,7 +102,10 @@ LM_LIB_PATH = Path(__file__).resolve().parent / "lib" / "libxotb200_lm.so"
 LM_DTYPE_BF16, LM_DTYPE_F32 = 0, 2
 LM_MIX_LATENT_ATTN, LM_MIX_DELTA_RULE, LM_MIX_ATTENTION, LM_MIX_GATED_DELTA = 0, 1, 2, 3
 LM_FF_RELU2, LM_FF_XIELU, LM_FF_MOE = 0, 1, 2
-LM_BLOCK_GROUP_RMS, LM_BLOCK_POST_LN = 0, 1
+LM_EXPERT_SILU_GATED, LM_EXPERT_RELU2 = 0, 1
+LM_ROUTER_SOFTMAX_ALL, LM_ROUTER_TOPK_SOFTMAX = 0, 1
+LM_BLOCK_GROUP_RMS, LM_BLOCK_POST_LN, LM_BLOCK_POST_RMS = 0, 1, 2
+LM_QKNORM_NONE, LM_QKNORM_HEAD, LM_QKNORM_ROW = 0, 1, 2
 LM_ROT_INTERLEAVED, LM_ROT_HALF = 0, 1
 
 
@@ -115,6 +118,9 @@ class LmLayer(C.Structure):
     ("kv_heads", C.c_int32), ("kv_from", C.c_int32), ("chunk", C.c_int32), ("qk_norm", C.c_int32), ("proj_bias", C.c_int32),
     ("dist_bias", C.c_int32), ("conv_taps", C.c_int32), ("ff_kind", C.c_int32), ("experts", C.c_int32), ("expert_ff", C.c_int32),
     ("top", C.c_int32), ("groups", C.c_int32), ("groups_keep", C.c_int32), ("softcap", C.c_float),
+    ("out_bias", C.c_int32), ("sink", C.c_int32), ("rel_buckets", C.c_int32), ("rel_max", C.c_float), ("q_temp_coef", C.c_float),
+    ("q_temp_every", C.c_int32), ("expert_act", C.c_int32), ("router_kind", C.c_int32), ("router_bias", C.c_int32),
+    ("shared_ff", C.c_int32),
   ]
 
 
@@ -122,6 +128,8 @@ class LmCfg(C.Structure):
   _fields_ = [
     ("n_layers", C.c_int32), ("start_layer", C.c_int32), ("end_layer", C.c_int32), ("width", C.c_int32), ("vocab", C.c_int32),
     ("norm_groups", C.c_int32), ("dtype", C.c_int32), ("norm_eps", C.c_float), ("block", C.c_int32), ("max_positions", C.c_int32),
+    ("pos_sinusoid", C.c_int32), ("sinusoid_base", C.c_float), ("embed_norm", C.c_int32), ("logit_scale", C.c_float),
+    ("logit_softcap", C.c_float),
   ]
 
 

@@ -88,14 +88,17 @@ struct LmLayer {
   size_t up, down;
   // grouped-query attention: columns of q / k / v (gate: c_g), bias vector over the projection's columns, norm weights, penalties
   int c_kk = 0, c_vv = 0;
-  size_t b_in = 0, q_norm = 0, k_norm = 0, r1 = 0, r2 = 0;
+  size_t b_in = 0, q_norm = 0, k_norm = 0, r1 = 0, r2 = 0, o_b = 0, sink = 0, rel = 0;
+  int rel_n = 0;                                       // distances tabulated for the learned bias: every distance >= rel_n - 1 is in the last bucket
+  int* rel_bucket = nullptr;                           // [rel_n] bucket of every tabulated distance (device; made on the host in double)
+  float* rel_tab = nullptr;                            // [heads][rel_n] the bias per head and distance (device; remade when weights change)
   int kv_src = -1;                                     // local index of the layer whose pool this layer reads (itself when it has keys/values)
   // gated delta rule: filter weights [channels, taps] (q, k, v channels in the projection's order), decay constants, column of beta
   size_t conv_w = 0, a_log = 0, dt_bias = 0;
   int c_b = 0, conv_ch = 0;
   size_t conv_off = 0;                                 // float offset of the filter inputs inside a slot's state block
   // feed-forward forms: xIELU parameters; mixture of experts: router [E, D], experts' [E][2 F, D] (gate rows, up rows) and [E][D, F]
-  size_t act_p = 0, router = 0, w_gu = 0, w_edown = 0;
+  size_t act_p = 0, router = 0, router_b = 0, w_gu = 0, w_edown = 0;   // a shared expert's matrices are `up` / `down`
   float* freqs = nullptr;                              // [rot_dims / 2] fp32 on the device
   void* pool = nullptr;                                // paged pool [n_pages * P, row] of T: latent + rotated key part, or keys + values
   size_t state_off = 0;                                // delta rules: float offset of this layer's state inside a slot's block
@@ -117,7 +120,9 @@ struct xotb200_lm {
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   char* blob = nullptr;
   size_t blob_elems = 0;
-  size_t embed = 0, final_norm = 0, head = 0;
+  size_t embed = 0, final_norm = 0, head = 0, embed_norm = 0;
+  float* pos_freqs = nullptr;                          // [ceil(width / 2)] frequencies of the computed position vector (device)
+  bool tables_stale = true;                            // tables derived from weights (learned distance bias) have to be remade
   std::map<std::string, Dest> dests;
   // request state
   int max_requests = 0, page_size = 0, n_pages = 0, pages_per_slot = 0;
@@ -182,11 +187,13 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
   const size_t al = 256 / e->esz;
   auto take = [&](size_t n) { size_t o = cur; cur = align_up(cur + n, al); return o; };
   auto dest = [&](const std::string& name, size_t off, int rows, int cols, int row_off) { e->dests[name] = Dest{off, rows, cols, row_off, false}; };
-  const bool post_ln = e->cfg.block == XOTB200_LM_BLOCK_POST_LN;
-  // the weight after a sublayer: a second grouped RMS norm ("norm1b"), or the bias of the closing layer norm ("norm1.b")
+  const bool post_ln = e->cfg.block == XOTB200_LM_BLOCK_POST_LN, post_rms = e->cfg.block == XOTB200_LM_BLOCK_POST_RMS;
+  // the weight after a sublayer: a second grouped RMS norm ("norm1b"), or the bias of the closing layer norm ("norm1.b"); a closing
+  // RMS norm has one weight only
   const std::string nb = post_ln ? ".b" : "b";
   if (e->first) {
     e->embed = take((size_t)V * D); dest("embed", e->embed, V, D, 0);
+    if (e->cfg.embed_norm) { e->embed_norm = take(D); dest("embed.norm", e->embed_norm, 1, D, 0); }
     if (e->cfg.max_positions > 0) { e->pos_table = take((size_t)e->cfg.max_positions * D); dest("pos", e->pos_table, e->cfg.max_positions, D, 0); }
   }
   for (int li = e->cfg.start_layer; li <= e->cfg.end_layer; ++li) {
@@ -196,7 +203,7 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
     const std::string p = "l" + std::to_string(li) + ".";
     REQUIRE(s.heads >= 1 && s.dim >= 1, "layer %d: heads and dim must be positive", li);
     L.norm1 = take(D); dest(p + "norm1", L.norm1, 1, D, 0);
-    L.norm1b = take(D); dest(p + "norm1" + nb, L.norm1b, 1, D, 0);
+    if (!post_rms) { L.norm1b = take(D); dest(p + "norm1" + nb, L.norm1b, 1, D, 0); }
     if (s.mixer == XOTB200_LM_MIX_LATENT_ATTN) {
       const int H = s.heads, dn = s.dim, dr = s.rot_dim, dv = s.vdim, R = s.kv_rank, HQ = H * (dn + dr);
       REQUIRE(R >= 1 && R <= 512, "layer %d: kv_rank %d outside 1..512", li, R);
@@ -263,6 +270,12 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
       REQUIRE(dv >= 1 && dv <= 256 && dk <= 1024, "layer %d: attention sizes dim %d (<= 1024) / vdim %d (1..256)", li, dk, dv);
       REQUIRE(s.window >= 0 && s.chunk >= 0 && s.softcap >= 0.f, "layer %d: negative window, chunk or softcap", li);
       REQUIRE(s.out_gate >= 0 && s.out_gate <= 2, "layer %d: unknown output gate %d", li, s.out_gate);
+      REQUIRE(s.qk_norm >= XOTB200_LM_QKNORM_NONE && s.qk_norm <= XOTB200_LM_QKNORM_ROW, "layer %d: unknown query/key norm %d", li, s.qk_norm);
+      REQUIRE(!s.out_bias || post_ln || post_rms, "layer %d: a bias of the output projection is added by the closing norm of the post-norm block forms only", li);
+      REQUIRE(s.q_temp_coef == 0.f || s.q_temp_every >= 1, "layer %d: query temperature every %d positions", li, s.q_temp_every);
+      REQUIRE(s.rel_buckets == 0 || (s.rel_buckets >= 2 && s.rel_buckets <= 65536 && s.rel_max > (float)(s.rel_buckets / 2) && s.rel_max <= 4194304.f),
+              "layer %d: %d distance buckets up to distance %g (2..65536 buckets, the largest distance above half their number and <= 4194304)", li,
+              s.rel_buckets, (double)s.rel_max);
       if (!own) {
         REQUIRE(s.kv_from >= e->cfg.start_layer && s.kv_from < li, "layer %d reads the keys/values of layer %d, which is not an earlier layer of this shard", li,
                 s.kv_from);
@@ -287,9 +300,14 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
         if (own) { dest(p + "mix.k.b", L.b_in + L.c_kk, 1, G * dk, 0); dest(p + "mix.v.b", L.b_in + L.c_vv, 1, G * dv, 0); }
       }
       if (s.qk_norm) {
-        L.q_norm = take(dk); dest(p + "mix.q.norm", L.q_norm, 1, dk, 0);
-        if (own) { L.k_norm = take(dk); dest(p + "mix.k.norm", L.k_norm, 1, dk, 0); }
+        const bool whole = s.qk_norm == XOTB200_LM_QKNORM_ROW;
+        const int nq = whole ? H * dk : dk, nk = whole ? G * dk : dk;
+        L.q_norm = take(nq); dest(p + "mix.q.norm", L.q_norm, 1, nq, 0);
+        if (own) { L.k_norm = take(nk); dest(p + "mix.k.norm", L.k_norm, 1, nk, 0); }
       }
+      if (s.out_bias) { L.o_b = take(D); dest(p + "mix.o.b", L.o_b, 1, D, 0); }
+      if (s.sink) { L.sink = take(H); dest(p + "mix.sink", L.sink, 1, H, 0); }
+      if (s.rel_buckets > 0) { L.rel = take((size_t)s.rel_buckets * H); dest(p + "mix.rel", L.rel, s.rel_buckets, H, 0); }
       if (s.dist_bias) {
         L.r1 = take(H); dest(p + "mix.r1", L.r1, 1, H, 0);
         L.r2 = take(H); dest(p + "mix.r2", L.r2, 1, H, 0);
@@ -337,7 +355,7 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
     const bool has_ff = s.ff_kind == XOTB200_LM_FF_MOE ? s.experts > 0 : s.ff > 0;
     if (has_ff) {
       L.norm2 = take(D); dest(p + "norm2", L.norm2, 1, D, 0);
-      L.norm2b = take(D); dest(p + "norm2" + nb, L.norm2b, 1, D, 0);
+      if (!post_rms) { L.norm2b = take(D); dest(p + "norm2" + nb, L.norm2b, 1, D, 0); }
     }
     if (s.ff_kind == XOTB200_LM_FF_MOE && has_ff) {
       const int E = s.experts, F = s.expert_ff;
@@ -345,15 +363,30 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
       if (s.groups > 1)
         REQUIRE(E % s.groups == 0 && s.groups_keep >= 1 && s.groups_keep <= s.groups && s.groups_keep * (E / s.groups) >= s.top,
                 "layer %d: %d experts in %d groups of which %d are kept cannot give %d experts per token", li, E, s.groups, s.groups_keep, s.top);
+      REQUIRE(s.expert_act == XOTB200_LM_EXPERT_SILU_GATED || s.expert_act == XOTB200_LM_EXPERT_RELU2, "layer %d: unknown expert form %d", li, s.expert_act);
+      REQUIRE(s.router_kind == XOTB200_LM_ROUTER_SOFTMAX_ALL || s.router_kind == XOTB200_LM_ROUTER_TOPK_SOFTMAX, "layer %d: unknown routing rule %d", li, s.router_kind);
+      REQUIRE(s.shared_ff >= 0, "layer %d: negative size of the shared expert", li);
+      const bool gated = s.expert_act == XOTB200_LM_EXPERT_SILU_GATED;
       L.router = take((size_t)E * D); dest(p + "mlp.router", L.router, E, D, 0);
-      L.w_gu = take((size_t)E * 2 * F * D);
+      if (s.router_bias) { L.router_b = take(E); dest(p + "mlp.router.b", L.router_b, 1, E, 0); }
+      L.w_gu = take((size_t)E * (gated ? 2 : 1) * F * D);
       L.w_edown = take((size_t)E * D * F);
       for (int x = 0; x < E; ++x) {
         const std::string ep = p + "mlp.e" + std::to_string(x) + ".";
-        dest(ep + "gate", L.w_gu, F, D, x * 2 * F);
-        dest(ep + "up", L.w_gu, F, D, x * 2 * F + (F % 8 ? F : 0));
-        if (F % 8 == 0) { e->dests[ep + "gate"].il8 = 0; e->dests[ep + "up"].il8 = 1; }   // gate and up rows interleaved in eights
+        if (gated) {
+          dest(ep + "gate", L.w_gu, F, D, x * 2 * F);
+          dest(ep + "up", L.w_gu, F, D, x * 2 * F + (F % 8 ? F : 0));
+          if (F % 8 == 0) { e->dests[ep + "gate"].il8 = 0; e->dests[ep + "up"].il8 = 1; }   // gate and up rows interleaved in eights
+        } else {
+          dest(ep + "up", L.w_gu, F, D, x * F);
+        }
         dest(ep + "down", L.w_edown, D, F, x * D);
+      }
+      if (s.shared_ff > 0) {
+        REQUIRE(!gated, "layer %d: a shared expert is implemented for relu^2 experts only", li);
+        L.up = take((size_t)s.shared_ff * D); dest(p + "mlp.shared.up", L.up, s.shared_ff, D, 0);
+        L.down = take((size_t)D * s.shared_ff); dest(p + "mlp.shared.down", L.down, D, s.shared_ff, 0);
+        e->max_ff = std::max(e->max_ff, s.shared_ff);
       }
       e->max_top = std::max(e->max_top, s.top);
       e->max_eff = std::max(e->max_eff, F);
@@ -369,7 +402,7 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
   }
   if (e->last) {
     e->final_norm = take(D); dest("final.norm", e->final_norm, 1, D, 0);
-    if (post_ln) { e->final_norm_b = take(D); dest("final.norm.b", e->final_norm_b, 1, D, 0); }
+    if (post_ln) { e->final_norm_b = take(D); dest("final.norm.b", e->final_norm_b, 1, D, 0); }   // a final RMS norm has a weight only
     e->head = take((size_t)V * D); dest("head", e->head, V, D, 0);
   }
   e->blob_elems = cur;
@@ -406,12 +439,13 @@ static int upload_tensor(xotb200_lm* e, Dest& d, const void* host_bf16) {
   CK(er);
   CK(er2);
   d.loaded = true;
+  e->tables_stale = true;
   return 0;
 }
 
 // does a tensor name belong to this shard? (so that an unknown name there is an error, and anything else is skipped)
 static bool owned_name(const xotb200_lm* e, const std::string& name) {
-  if (name == "embed" || name == "pos") return e->first;
+  if (name == "embed" || name == "pos" || name == "embed.norm") return e->first;
   if (name == "head" || name == "final.norm" || name == "final.norm.b") return e->last;
   if (name.size() > 1 && name[0] == 'l' && isdigit((unsigned char)name[1])) {
     const int li = atoi(name.c_str() + 1);
@@ -838,13 +872,22 @@ static int gqa_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
   const Paging pg{e->d_table, e->pages_per_slot, e->page_size};
   T* pool = static_cast<T*>(e->layers[L.kv_src].pool);
   const int slots = H + (own ? 2 * G : 0);
-  gqa_prepare_kernel<T><<<cdiv((long)M * slots, 8), 256, 0, e->stream>>>(
-      e->proj, L.n_in, L.c_q, L.c_kk, L.c_vv, s.proj_bias ? at<T>(e, L.b_in) : nullptr, s.qk_norm ? at<T>(e, L.q_norm) : nullptr,
-      s.qk_norm && own ? at<T>(e, L.k_norm) : nullptr, e->cfg.norm_eps, H, G, dk, dv, own ? 1 : 0, sp.row_slot, sp.row_pos, pg, pool, e->qfull,
-      sp.n_gqa_tiles > 0 ? static_cast<bf16*>(e->q16) : nullptr, M);
+  bf16* q16 = sp.n_gqa_tiles > 0 ? static_cast<bf16*>(e->q16) : nullptr;
+  if (s.qk_norm == XOTB200_LM_QKNORM_ROW) {
+    const int nt = std::min(1024, std::max(128, cdiv(H * dk, 4 * 32) * 32));
+    gqa_prepare_row_kernel<T><<<M, nt, 0, e->stream>>>(e->proj, L.n_in, L.c_q, L.c_kk, L.c_vv, s.proj_bias ? at<T>(e, L.b_in) : nullptr, at<T>(e, L.q_norm),
+                                                        own ? at<T>(e, L.k_norm) : nullptr, e->cfg.norm_eps, H, G, dk, dv, own ? 1 : 0, s.q_temp_coef,
+                                                        s.q_temp_every, sp.row_slot, sp.row_pos, pg, pool, e->qfull, q16);
+  } else {
+    gqa_prepare_kernel<T><<<cdiv((long)M * slots, 8), 256, 0, e->stream>>>(
+        e->proj, L.n_in, L.c_q, L.c_kk, L.c_vv, s.proj_bias ? at<T>(e, L.b_in) : nullptr, s.qk_norm ? at<T>(e, L.q_norm) : nullptr,
+        s.qk_norm && own ? at<T>(e, L.k_norm) : nullptr, e->cfg.norm_eps, H, G, dk, dv, own ? 1 : 0, s.q_temp_coef, s.q_temp_every, sp.row_slot, sp.row_pos,
+        pg, pool, e->qfull, q16, M);
+  }
   CK(cudaGetLastError());
   e->launches++;
-  const GqaScore sc{s.scale, s.softcap, s.window, s.chunk, s.dist_bias ? at<T>(e, L.r1) : nullptr, s.dist_bias ? at<T>(e, L.r2) : nullptr};
+  const GqaScore sc{s.scale, s.softcap, s.window, s.chunk, s.dist_bias ? at<T>(e, L.r1) : nullptr, s.dist_bias ? at<T>(e, L.r2) : nullptr,
+                    s.rel_buckets > 0 ? L.rel_tab : nullptr, L.rel_n, s.sink ? at<T>(e, L.sink) : nullptr};
   const float* gate = s.out_gate ? e->proj : nullptr;
   const int qpi = gqa_rows_per_item(s);
   const auto& it = sp.items.at(-qpi);   // the lists of this mixer have negative keys
@@ -870,8 +913,8 @@ static int gqa_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
     CK(cudaGetLastError());
     e->launches++;
     if (splits > 1) {
-      gqa_combine_kernel<T><<<dim3(it.second, cdiv(qpi * H, 8)), 256, 0, e->stream>>>(e->part, it.first, H, dv, splits, gate, s.out_gate, L.n_in, L.c_g,
-                                                                                     static_cast<T*>(e->oh));
+      gqa_combine_kernel<T><<<dim3(it.second, cdiv(qpi * H, 8)), 256, 0, e->stream>>>(e->part, it.first, H, dv, splits, s.sink ? at<T>(e, L.sink) : nullptr, gate,
+                                                                                     s.out_gate, L.n_in, L.c_g, static_cast<T*>(e->oh));
       CK(cudaGetLastError());
       e->launches++;
     }
@@ -969,17 +1012,25 @@ static int feed_forward(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
   T* h = static_cast<T*>(e->h);
   if (s.ff_kind == XOTB200_LM_FF_MOE) {
     const int E = s.experts, F = s.expert_ff, top = s.top;
+    const bool gated = s.expert_act == XOTB200_LM_EXPERT_SILU_GATED;
+    const int shared = s.shared_ff > 0 ? 1 : 0;
+    if (shared) {
+      // the shared expert first: y = W_down relu(W_up h)^2; the chosen experts' weighted outputs are then added to it
+      TRY((product<T, T, T, 1>(e, h, D, 0, at<T>(e, L.up), D, 1, 0, static_cast<T*>(e->act), s.shared_ff, 0, M, s.shared_ff, D, 1)));
+      TRY((product<T, T, float, 0>(e, static_cast<T*>(e->act), s.shared_ff, 0, at<T>(e, L.down), s.shared_ff, 1, 0, e->y, D, 0, M, D, s.shared_ff, 1)));
+    }
     {
       auto kern = moe_router_kernel<T>;
       const size_t rsm = ((size_t)((D + 3) & ~3) + E) * 4;
       TRY(opt_in_smem(kern, rsm));
-      kern<<<M, std::min(1024, std::max(64, cdiv(E, 2) * 32)), rsm, e->stream>>>(h, D, at<T>(e, L.router), E, s.groups, s.groups_keep, top, e->moe_ids, e->moe_wts, M);
+      kern<<<M, std::min(1024, std::max(64, cdiv(E, 2) * 32)), rsm, e->stream>>>(h, D, at<T>(e, L.router), s.router_bias ? at<T>(e, L.router_b) : nullptr,
+                                                                                 s.router_kind, E, s.groups, s.groups_keep, top, e->moe_ids, e->moe_wts, M);
     }
     CK(cudaGetLastError());
     e->launches++;
-    const int il8 = F % 8 == 0 ? 1 : 0;
+    const int il8 = gated && F % 8 == 0 ? 1 : 0;
     if constexpr (std::is_same<T, bf16>::value) {
-      if (M >= MOE_GROUPED_MIN_ROWS && e->gemm_mode != 1 && il8 && D % 8 == 0) {
+      if (M >= MOE_GROUPED_MIN_ROWS && e->gemm_mode != 1 && F % 8 == 0 && D % 8 == 0) {
         const int pairs = M * top, tiles = cdiv(pairs, LTC_M) + E, m_pad = tiles * LTC_M;
         REQUIRE(tiles <= e->moe_tiles_cap, "internal: the expert tile list was not sized for this step");
         int *counts = e->moe_plan, *starts = counts + e->max_experts, *cursor = starts + e->max_experts + 1, *place = cursor + e->max_experts,
@@ -990,12 +1041,13 @@ static int feed_forward(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
         moe_scatter_kernel<bf16><<<cdiv(pairs, 8), 256, 0, e->stream>>>(h, D, e->moe_ids, pairs, top, starts, cursor, place, xg);
         CK(cudaGetLastError());
         e->launches += 3;
-        int r = grouped_product<3, bf16>(e, xg, D, at<bf16>(e, L.w_gu), D, (long)2 * F * D, E, static_cast<bf16*>(e->mact), F, m_pad, 2 * F, D, tile_expert);
+        int r = gated ? grouped_product<3, bf16>(e, xg, D, at<bf16>(e, L.w_gu), D, (long)2 * F * D, E, static_cast<bf16*>(e->mact), F, m_pad, 2 * F, D, tile_expert)
+                      : grouped_product<1, bf16>(e, xg, D, at<bf16>(e, L.w_gu), D, (long)F * D, E, static_cast<bf16*>(e->mact), F, m_pad, F, D, tile_expert);
         if (r < 0) return r;
         if (r == 1) r = grouped_product<0, float>(e, static_cast<bf16*>(e->mact), F, at<bf16>(e, L.w_edown), F, (long)D * F, E, e->moe_yg, D, m_pad, D, F, tile_expert);
         if (r < 0) return r;
         if (r == 1) {
-          moe_combine_kernel<<<M, 256, 0, e->stream>>>(e->moe_yg, place, e->moe_wts, top, D, e->y);
+          moe_combine_kernel<<<M, 256, 0, e->stream>>>(e->moe_yg, place, e->moe_wts, top, D, shared, e->y);
           CK(cudaGetLastError());
           e->launches++;
           return 0;
@@ -1005,7 +1057,7 @@ static int feed_forward(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
     {
       auto kern = moe_rows_up_kernel<T>;
       TRY(opt_in_smem(kern, (size_t)D * 4));
-      kern<<<dim3(M, top, std::max(1, std::min(cdiv(F, 8), M <= 16 ? 1024 : 16))), 256, (size_t)D * 4, e->stream>>>(h, D, at<T>(e, L.w_gu), F, il8, e->moe_ids, top, static_cast<T*>(e->mact));
+      kern<<<dim3(M, top, std::max(1, std::min(cdiv(F, 8), M <= 16 ? 1024 : 16))), 256, (size_t)D * 4, e->stream>>>(h, D, at<T>(e, L.w_gu), F, il8, gated ? 1 : 0, e->moe_ids, top, static_cast<T*>(e->mact));
       CK(cudaGetLastError());
       e->launches++;
     }
@@ -1013,7 +1065,7 @@ static int feed_forward(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
       auto kern = moe_rows_down_kernel<T>;
       TRY(opt_in_smem(kern, (size_t)top * F * 4));
       kern<<<dim3(M, std::max(1, std::min(cdiv(D, 8), M <= 16 ? 1024 : 16))), 256, (size_t)top * F * 4, e->stream>>>(static_cast<T*>(e->mact), F, at<T>(e, L.w_edown), D, e->moe_ids, e->moe_wts,
-                                                                                                   top, e->y);
+                                                                                                   top, shared, e->y);
       CK(cudaGetLastError());
       e->launches++;
     }
@@ -1037,24 +1089,42 @@ static int run_mixer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
   }
 }
 
-// layers of the form x += LN(sublayer(x)): the sublayer reads the stream itself (its T copy h), a layer norm closes it
+static void finish_logits(xotb200_lm* e, int n_want) {
+  const float scale = e->cfg.logit_scale != 0.f ? e->cfg.logit_scale : 1.0f;
+  argmax_rows_kernel<<<n_want, 1024, 0, e->stream>>>(e->logits, e->cfg.vocab, scale, e->cfg.logit_softcap, e->d_argmax);
+  e->launches++;
+}
+
+// layers of the form x += norm(sublayer(x)): the sublayer reads the stream itself (its T copy h); a layer norm (weight and bias)
+// or an RMS norm (weight stored around zero) closes it and adds the bias of the mixer's output projection on the way
 template <typename T>
-static int run_layers_post_ln(xotb200_lm* e, const StepPlan& sp, int n_want) {
+static int run_layers_post(xotb200_lm* e, const StepPlan& sp, int n_want) {
   const int D = e->cfg.width, M = sp.M;
   const float eps = e->cfg.norm_eps;
+  const bool rms = e->cfg.block == XOTB200_LM_BLOCK_POST_RMS;
   T* h = static_cast<T*>(e->h);
   const int nt = std::min(1024, std::max(128, cdiv(D, 4 * 32) * 32));
   auto kern = residual_layernorm_kernel<T>;
+  auto kern_rms = residual_rmsnorm_kernel<T>;
   TRY(opt_in_smem(kern, (size_t)D * 4));
-  auto close = [&](size_t w, size_t b) -> int {
-    kern<<<M, nt, (size_t)D * 4, e->stream>>>(e->x, e->y, at<T>(e, w), at<T>(e, b), h, nullptr, D, eps);
+  TRY(opt_in_smem(kern_rms, (size_t)D * 4));
+  auto close = [&](size_t w, size_t b, const T* y_bias) -> int {
+    if (rms) kern_rms<<<M, nt, (size_t)D * 4, e->stream>>>(e->x, e->y, y_bias, at<T>(e, w), 1.0f, h, nullptr, D, eps);
+    else kern<<<M, nt, (size_t)D * 4, e->stream>>>(e->x, e->y, y_bias, at<T>(e, w), at<T>(e, b), h, nullptr, D, eps);
     CK(cudaGetLastError());
     e->launches++;
     return 0;
   };
   if (e->first) {
-    embed_pos_rows_kernel<T><<<M, 128, 0, e->stream>>>(at<T>(e, e->embed), e->cfg.max_positions > 0 ? at<T>(e, e->pos_table) : nullptr, sp.tokens, sp.row_pos,
-                                                       e->x, h, D);
+    if (e->cfg.pos_sinusoid || e->cfg.embed_norm) {
+      auto ek = embed_sinusoid_rows_kernel<T>;
+      TRY(opt_in_smem(ek, (size_t)D * 4));
+      ek<<<M, nt, (size_t)D * 4, e->stream>>>(at<T>(e, e->embed), e->cfg.max_positions > 0 ? at<T>(e, e->pos_table) : nullptr, e->pos_freqs, sp.tokens, sp.row_pos,
+                                              e->cfg.embed_norm ? at<T>(e, e->embed_norm) : nullptr, 1.0f, eps, e->x, h, D);
+    } else {
+      embed_pos_rows_kernel<T><<<M, 128, 0, e->stream>>>(at<T>(e, e->embed), e->cfg.max_positions > 0 ? at<T>(e, e->pos_table) : nullptr, sp.tokens, sp.row_pos,
+                                                         e->x, h, D);
+    }
   } else {
     cast_rows_kernel<T><<<std::min(4096, cdiv((long)M * D, 256)), 256, 0, e->stream>>>(e->x, h, (size_t)M * D);
   }
@@ -1063,23 +1133,23 @@ static int run_layers_post_ln(xotb200_lm* e, const StepPlan& sp, int n_want) {
   for (size_t li = 0; li < e->layers.size(); ++li) {
     LmLayer& L = e->layers[li];
     TRY(run_mixer<T>(e, L, sp));
-    TRY(close(L.norm1, L.norm1b));
+    TRY(close(L.norm1, L.norm1b, L.s.mixer == XOTB200_LM_MIX_ATTENTION && L.s.out_bias ? at<T>(e, L.o_b) : nullptr));
     if (layer_has_ff(L.s)) {
       TRY(feed_forward<T>(e, L, sp));
-      TRY(close(L.norm2, L.norm2b));
+      TRY(close(L.norm2, L.norm2b, nullptr));
     }
     if (e->trace) CK(cudaMemcpyAsync(e->trace_buf + li * (size_t)M * D, e->x, (size_t)M * D * 4, cudaMemcpyDeviceToDevice, e->stream));
   }
   if (e->trace) e->trace_floats = e->layers.size() * (size_t)M * D;
   if (e->last && n_want > 0) {
     T* hw = static_cast<T*>(e->hw);
-    kern<<<n_want, nt, (size_t)D * 4, e->stream>>>(e->x, nullptr, at<T>(e, e->final_norm), at<T>(e, e->final_norm_b), hw, sp.want, D, eps);
+    if (rms) kern_rms<<<n_want, nt, (size_t)D * 4, e->stream>>>(e->x, nullptr, nullptr, at<T>(e, e->final_norm), 1.0f, hw, sp.want, D, eps);
+    else kern<<<n_want, nt, (size_t)D * 4, e->stream>>>(e->x, nullptr, nullptr, at<T>(e, e->final_norm), at<T>(e, e->final_norm_b), hw, sp.want, D, eps);
     CK(cudaGetLastError());
     e->launches++;
     TRY((product<T, T, float, 0>(e, hw, D, 0, at<T>(e, e->head), D, 1, 0, e->logits, e->cfg.vocab, 0, n_want, e->cfg.vocab, D, 1)));
-    argmax_rows_kernel<<<n_want, 1024, 0, e->stream>>>(e->logits, e->cfg.vocab, e->d_argmax);
+    finish_logits(e, n_want);
     CK(cudaGetLastError());
-    e->launches++;
   }
   return 0;
 }
@@ -1093,7 +1163,7 @@ static int norm_threads(int D, int G) {
 
 template <typename T>
 static int run_layers(xotb200_lm* e, const StepPlan& sp, int n_want) {
-  if (e->cfg.block == XOTB200_LM_BLOCK_POST_LN) return run_layers_post_ln<T>(e, sp, n_want);
+  if (e->cfg.block != XOTB200_LM_BLOCK_GROUP_RMS) return run_layers_post<T>(e, sp, n_want);
   const int D = e->cfg.width, G = e->cfg.norm_groups, M = sp.M;
   const float eps = e->cfg.norm_eps;
   T* h = static_cast<T*>(e->h);
@@ -1139,9 +1209,8 @@ static int run_layers(xotb200_lm* e, const StepPlan& sp, int n_want) {
     CK(cudaGetLastError());
     e->launches++;
     TRY((product<T, T, float, 0>(e, hw, D, 0, at<T>(e, e->head), D, 1, 0, e->logits, e->cfg.vocab, 0, n_want, e->cfg.vocab, D, 1)));
-    argmax_rows_kernel<<<n_want, 1024, 0, e->stream>>>(e->logits, e->cfg.vocab, e->d_argmax);
+    finish_logits(e, n_want);
     CK(cudaGetLastError());
-    e->launches++;
   }
   return 0;
 }
@@ -1170,8 +1239,14 @@ int xotb200_lm_create(const xotb200_lm_cfg* cfg, const xotb200_lm_layer* layers,
           "bad layer range [%d, %d] of %d", cfg->start_layer, cfg->end_layer, cfg->n_layers);
   REQUIRE(cfg->width >= 1 && cfg->vocab >= 1, "width and vocab must be positive");
   REQUIRE(cfg->norm_groups >= 1 && cfg->width % cfg->norm_groups == 0, "width %d is not a multiple of norm_groups %d", cfg->width, cfg->norm_groups);
-  REQUIRE(cfg->block == XOTB200_LM_BLOCK_GROUP_RMS || cfg->block == XOTB200_LM_BLOCK_POST_LN, "unknown block form %d", cfg->block);
+  REQUIRE(cfg->block == XOTB200_LM_BLOCK_GROUP_RMS || cfg->block == XOTB200_LM_BLOCK_POST_LN || cfg->block == XOTB200_LM_BLOCK_POST_RMS,
+          "unknown block form %d", cfg->block);
   REQUIRE(cfg->max_positions >= 0, "negative max_positions");
+  REQUIRE(cfg->block != XOTB200_LM_BLOCK_GROUP_RMS || (!cfg->pos_sinusoid && !cfg->embed_norm),
+          "a computed position vector and a norm on the embedding belong to the post-norm block forms");
+  REQUIRE(!cfg->embed_norm || cfg->block == XOTB200_LM_BLOCK_POST_RMS, "the norm on the embedding is the RMS norm of the post-RMS block form");
+  REQUIRE(!cfg->pos_sinusoid || cfg->sinusoid_base > 0.f, "the computed position vector needs a positive base");
+  REQUIRE(cfg->logit_softcap >= 0.f, "negative logit soft cap");
   int ndev = 0;
   CK(cudaGetDeviceCount(&ndev));
   REQUIRE(device >= 0 && device < ndev, "device %d out of range (%d visible)", device, ndev);
@@ -1212,8 +1287,55 @@ int xotb200_lm_create(const xotb200_lm_cfg* cfg, const xotb200_lm_layer* layers,
       return fail(XOTB200_ECUDA);
     }
   }
+  if (e->first && cfg->pos_sinusoid) {
+    const int n = (cfg->width + 1) / 2;
+    std::vector<float> f(n);
+    for (int i = 0; i < n; ++i) f[i] = (float)pow((double)cfg->sinusoid_base, -2.0 * i / cfg->width);
+    if (cudaMalloc(&e->pos_freqs, (size_t)n * 4) != cudaSuccess ||
+        cudaMemcpyAsync(e->pos_freqs, f.data(), (size_t)n * 4, cudaMemcpyHostToDevice, e->stream) != cudaSuccess ||
+        cudaStreamSynchronize(e->stream) != cudaSuccess) {
+      set_err("position frequency table allocation failed");
+      return fail(XOTB200_ECUDA);
+    }
+  }
+  for (auto& L : e->layers) {
+    if (L.s.mixer != XOTB200_LM_MIX_ATTENTION || L.s.rel_buckets <= 0) continue;
+    // bucket of every distance up to the first one that falls into the last bucket (all larger distances do too), in double
+    const int B = L.s.rel_buckets, half = B / 2;
+    const double span = log((double)L.s.rel_max / half);
+    std::vector<int> bk;
+    for (int n = 0;; ++n) {
+      int b = n;
+      if (n >= half) b = std::min(B - 1, half + (int)floor(log((double)n / half) / span * (B - half)));
+      bk.push_back(b);
+      if (b == B - 1) break;
+    }
+    L.rel_n = (int)bk.size();
+    if (cudaMalloc(&L.rel_bucket, bk.size() * 4) != cudaSuccess || cudaMalloc(&L.rel_tab, bk.size() * L.s.heads * 4) != cudaSuccess ||
+        cudaMemcpyAsync(L.rel_bucket, bk.data(), bk.size() * 4, cudaMemcpyHostToDevice, e->stream) != cudaSuccess ||
+        cudaStreamSynchronize(e->stream) != cudaSuccess) {
+      set_err("distance bucket table allocation failed");
+      return fail(XOTB200_ECUDA);
+    }
+  }
   cudaStreamSynchronize(e->stream);
   *out = e;
+  return 0;
+}
+
+// tables that are functions of weights: the learned distance bias per head and distance.  Remade before the first step after any
+// weight has changed; never inside a captured step.
+static int refresh_tables(xotb200_lm* e) {
+  if (!e->tables_stale) return 0;
+  for (auto& L : e->layers) {
+    if (!L.rel_tab) continue;
+    const long n = (long)L.s.heads * L.rel_n;
+    if (e->esz == 2) gqa_rel_table_kernel<bf16><<<cdiv(n, 256), 256, 0, e->stream>>>(at<bf16>(e, L.rel), L.rel_bucket, L.s.heads, L.rel_n, L.rel_tab);
+    else gqa_rel_table_kernel<float><<<cdiv(n, 256), 256, 0, e->stream>>>(at<float>(e, L.rel), L.rel_bucket, L.s.heads, L.rel_n, L.rel_tab);
+    CK(cudaGetLastError());
+    e->launches++;
+  }
+  e->tables_stale = false;
   return 0;
 }
 
@@ -1223,9 +1345,12 @@ int xotb200_lm_destroy(xotb200_lm* e) {
   if (e->stream) cudaStreamSynchronize(e->stream);
   drop_graphs(e);
   free_state(e);
-  for (auto& L : e->layers)
+  for (auto& L : e->layers) {
     if (L.freqs) cudaFree(L.freqs);
-  void* ptrs[] = {e->dist_tab, e->moe_xg, e->moe_yg, e->moe_plan, e->dkk, e->drr, e->cvb, e->moe_ids, e->moe_wts, e->mact, e->du, e->dau, e->part, e->q16, e->cbuf, e->knx, e->vxx, e->blob, e->d_stage, e->x, e->y, e->proj, e->qraw, e->qfull, e->wlog, e->oraw, e->logits, e->h, e->cqn, e->qn, e->olat, e->oh, e->act,
+    if (L.rel_bucket) cudaFree(L.rel_bucket);
+    if (L.rel_tab) cudaFree(L.rel_tab);
+  }
+  void* ptrs[] = {e->pos_freqs, e->dist_tab, e->moe_xg, e->moe_yg, e->moe_plan, e->dkk, e->drr, e->cvb, e->moe_ids, e->moe_wts, e->mact, e->du, e->dau, e->part, e->q16, e->cbuf, e->knx, e->vxx, e->blob, e->d_stage, e->x, e->y, e->proj, e->qraw, e->qfull, e->wlog, e->oraw, e->logits, e->h, e->cqn, e->qn, e->olat, e->oh, e->act,
                   e->th, e->hw, e->d_argmax, e->trace_buf};
   for (void* p : ptrs)
     if (p) cudaFree(p);
@@ -1269,7 +1394,9 @@ int xotb200_lm_init_synthetic(xotb200_lm* e, uint64_t seed) {
     const size_t n = (size_t)d.rows * d.cols, off = d.elem_off + (size_t)d.row_off * d.cols + (d.il8 == 1 ? n : 0);   // interleaved pairs: any split will do
     float mean = 0.f, dev = 1.0f / sqrtf((float)d.cols);
     const auto ends = [&](const char* suf) { const size_t n = strlen(suf); return name.size() >= n && name.compare(name.size() - n, n, suf) == 0; };
-    if (ends(".r1")) { mean = 0.1f; dev = 0.03f; }              // distance penalties stay positive
+    const bool block_norm = name.find(".mix.") == std::string::npos && name.find("norm") != std::string::npos;
+    if (block_norm && e->cfg.block == XOTB200_LM_BLOCK_POST_RMS) dev = 0.1f;   // closing RMS norms: weights stored around zero
+    else if (ends(".r1")) { mean = 0.1f; dev = 0.03f; }              // distance penalties stay positive
     else if (ends(".r2")) { mean = 1.f; dev = 0.2f; }
     else if (ends(".b") && d.rows == 1) dev = 0.1f;            // biases of projections and layer norms
     else if (ends(".A_log")) dev = 0.3f;
@@ -1290,6 +1417,7 @@ int xotb200_lm_init_synthetic(xotb200_lm* e, uint64_t seed) {
     }
     d.loaded = true;
   }
+  e->tables_stale = true;
   CK(cudaStreamSynchronize(e->stream));
   return 0;
 }
@@ -1451,6 +1579,7 @@ int xotb200_lm_step(xotb200_lm* e, int n_seq, const int32_t* slots, const int32_
   if (e->first)
     for (long m = 0; m < M; ++m) REQUIRE(tokens[m] >= 0 && tokens[m] < V, "token id %d outside the vocabulary of %d", tokens[m], V);
   TRY(ensure_scratch(e, (int)M, n_want));
+  TRY(refresh_tables(e));
   // ---- commit: pages and lengths; the step's index arrays are built in one host vector and copied once
   const bool use_flash = e->esz == 2 && e->flash_on && e->flash_fits;
   std::vector<int> qpis, windows;

@@ -1,6 +1,7 @@
-// layered_blocks.cuh — device code of the layered-model engine for models whose layers are  x += LN(sublayer(x))  (the sublayer
-// reads the residual stream itself, a layer norm with weight and bias closes it), with a learned position table, short causal
-// convolutions in front of a gated delta rule, the two-sided xIELU activation and mixtures of gated experts.
+// layered_blocks.cuh — device code of the layered-model engine for models whose layers are  x += norm(sublayer(x))  (the sublayer
+// reads the residual stream itself; a layer norm with weight and bias, or an RMS norm with a weight stored around zero, closes it),
+// with a learned position table or a computed sine/cosine position vector, short causal convolutions in front of a gated delta
+// rule, the two-sided xIELU activation and mixtures of experts (gated silu or relu^2 experts, two routing rules).
 //
 // Number formats as in layered_kernels.cuh: T is the storage type of weights and GEMM inputs (bf16 serving, float in the 32-bit
 // mode); the residual stream, norms, router, decays, step sizes, unit vectors and every state are fp32 whatever T is.
@@ -44,26 +45,90 @@ __global__ void cast_rows_kernel(const float* __restrict__ x, T* __restrict__ h,
 }
 
 // ---------------------------------------------------------------------------------------------------------------------------
-// Layer norm that closes a sublayer:   x[m] += (y[m] - mean) / sqrt(var + eps) * w + b ;   h[m] = T(x[m])     (y != NULL)
+// Layer norm that closes a sublayer:   x[m] += (t - mean) / sqrt(var + eps) * w + b,  t = y[m] + y_bias ;   h[m] = T(x[m])     (y != NULL)
 // or norms gathered rows of the stream: h[m] = T((x[src_rows[m]] - mean) / sqrt(var + eps) * w + b)            (y == NULL)
 // var = mean of the squared deviations (two passes over the row, which waits in shared memory).  One block per row;
 // dynamic shared memory: D floats.
 // ---------------------------------------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void residual_layernorm_kernel(float* __restrict__ x, const float* __restrict__ y, const T* __restrict__ w, const T* __restrict__ b,
-                                          T* __restrict__ h, const int* __restrict__ src_rows, int D, float eps) {
+__global__ void residual_layernorm_kernel(float* __restrict__ x, const float* __restrict__ y, const T* __restrict__ y_bias, const T* __restrict__ w,
+                                          const T* __restrict__ b, T* __restrict__ h, const int* __restrict__ src_rows, int D, float eps) {
   extern __shared__ float ln_row[];
   __shared__ float red[32];
   const int m = blockIdx.x;
   const float* in = y ? y + (size_t)m * D : x + (size_t)(src_rows ? src_rows[m] : m) * D;
   float s = 0.f;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) { const float v = in[d]; ln_row[d] = v; s += v; }
+  for (int d = threadIdx.x; d < D; d += blockDim.x) { const float v = in[d] + (y && y_bias ? ldf(y_bias + d) : 0.f); ln_row[d] = v; s += v; }
   const float mean = block_sum(s, red) / (float)D;
   float q = 0.f;
   for (int d = threadIdx.x; d < D; d += blockDim.x) { const float c = ln_row[d] - mean; q = fmaf(c, c, q); }
   const float rstd = 1.0f / sqrtf(block_sum(q, red) / (float)D + eps);
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float v = (ln_row[d] - mean) * rstd * ldf(w + d) + ldf(b + d);
+    if (y) {
+      v += x[(size_t)m * D + d];
+      x[(size_t)m * D + d] = v;
+    }
+    if (h) stf(h + (size_t)m * D + d, v);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// embedding with a computed position vector:  e[d] = embed[token[m], d] + (d even ? sin : cos)(row_pos[m] * freqs[d / 2]), the
+// angle in fp32 (freqs are rounded once from double on the host; NULL = no such vector), + pos_table[row_pos[m], d] when there is
+// a learned table; then, when w_norm != NULL, the RMS norm x = e / sqrt(mean(e^2) + eps) * (w_offset + w_norm).  Writes the fp32
+// stream x and its T copy h.  One block per row; dynamic shared memory: D floats.
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_sinusoid_rows_kernel(const T* __restrict__ embed, const T* __restrict__ pos_table, const float* __restrict__ freqs,
+                                           const int* __restrict__ tokens, const int* __restrict__ row_pos, const T* __restrict__ w_norm, float w_offset,
+                                           float eps, float* __restrict__ x, T* __restrict__ h, int D) {
+  extern __shared__ float ln_row[];
+  __shared__ float red[32];
+  const int m = blockIdx.x;
+  const T* src = embed + (size_t)tokens[m] * D;
+  const T* ps = pos_table ? pos_table + (size_t)row_pos[m] * D : nullptr;
+  const float p = (float)row_pos[m];
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float v = ldf(src + d) + (ps ? ldf(ps + d) : 0.f);
+    if (freqs) {
+      const float ang = p * freqs[d >> 1];
+      v += (d & 1) ? cosf(ang) : sinf(ang);
+    }
+    ln_row[d] = v;                                             // read back by the same thread only
+    ss = fmaf(v, v, ss);
+  }
+  const float r = w_norm ? 1.0f / sqrtf(block_sum(ss, red) / (float)D + eps) : 1.0f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    const float v = w_norm ? ln_row[d] * r * (w_offset + ldf(w_norm + d)) : ln_row[d];
+    x[(size_t)m * D + d] = v;
+    if (h) stf(h + (size_t)m * D + d, v);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// RMS norm that closes a sublayer:   t = y[m] + y_bias ;  x[m] += t / sqrt(mean(t^2) + eps) * (w_offset + w) ;  h[m] = T(x[m])
+// or norms gathered rows of the stream: h[m] = T(x[src_rows[m]] / sqrt(mean(.^2) + eps) * (w_offset + w))        (y == NULL)
+// w_offset = 1 for weights stored around zero, 0 for plain weights; y_bias (may be NULL) is the bias of the projection that made
+// y, added here so that it costs no pass of its own.  One block per row; dynamic shared memory: D floats.
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void residual_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ y, const T* __restrict__ y_bias, const T* __restrict__ w,
+                                        float w_offset, T* __restrict__ h, const int* __restrict__ src_rows, int D, float eps) {
+  extern __shared__ float ln_row[];
+  __shared__ float red[32];
+  const int m = blockIdx.x;
+  const float* in = y ? y + (size_t)m * D : x + (size_t)(src_rows ? src_rows[m] : m) * D;
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    const float v = in[d] + (y && y_bias ? ldf(y_bias + d) : 0.f);
+    ln_row[d] = v;                                             // read back by the same thread only
+    ss = fmaf(v, v, ss);
+  }
+  const float r = 1.0f / sqrtf(block_sum(ss, red) / (float)D + eps);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float v = ln_row[d] * r * (w_offset + ldf(w + d));
     if (y) {
       v += x[(size_t)m * D + d];
       x[(size_t)m * D + d] = v;
@@ -214,14 +279,17 @@ __device__ __forceinline__ void row_dot4(const T* const (&w)[4], const float* co
 }
 
 // ---------------------------------------------------------------------------------------------------------------------------
-// Mixture of experts, router: logits z = W_r h in fp32 (h in T), scores s = softmax(z) over all E experts; experts form `groups`
-// equal groups of neighbours, a group's score is its best expert's, only experts of the `keep` best groups can be chosen; the
-// `top` best of those are the token's experts, weighted by their s (not renormalised).  Ties go to the lower index.
-// One block per row (its warps share the experts' logits, warp 0 selects); dynamic shared memory: D + E floats.
+// Mixture of experts, router: logits z = W_r h (+ bias) in fp32 (h in T).
+//   kind 0: scores s = softmax(z) over all E experts; experts form `groups` equal groups of neighbours, a group's score is its best
+//           expert's, only experts of the `keep` best groups can be chosen; the `top` best of those are the token's experts,
+//           weighted by their s (not renormalised);
+//   kind 1: the `top` largest logits are the token's experts, weighted by the softmax over those `top` logits only.
+// Ties go to the lower index.  One block per row (its warps share the experts' logits, warp 0 selects); dynamic shared memory:
+// D + E floats.
 // ---------------------------------------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void moe_router_kernel(const T* __restrict__ h, int D, const T* __restrict__ w_router, int E, int groups, int keep, int top,
-                                  int* __restrict__ ids, float* __restrict__ wts, int M) {
+__global__ void moe_router_kernel(const T* __restrict__ h, int D, const T* __restrict__ w_router, const T* __restrict__ bias, int kind, int E,
+                                  int groups, int keep, int top, int* __restrict__ ids, float* __restrict__ wts, int M) {
   extern __shared__ __align__(16) float rsm[];                 // [D] the row (fp32), then [E] scores
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const int m = blockIdx.x;
@@ -232,10 +300,29 @@ __global__ void moe_router_kernel(const T* __restrict__ h, int D, const T* __res
   const bool vec = D % (16 / sizeof(T)) == 0 && (reinterpret_cast<uintptr_t>(w_router) & 15) == 0;
   for (int e = warp; e < E; e += nw) {                         // the warps share the experts; logits in fp32
     const float z = row_dot(w_router + (size_t)e * D, hs, D, lane, vec);
-    if (lane == 0) s[e] = z;
+    if (lane == 0) s[e] = z + (bias ? ldf(bias + e) : 0.f);
   }
   __syncthreads();
   if (warp != 0) return;
+  if (kind == 1) {
+    if (lane == 0) {
+      float den = 0.f, first = 0.f;
+      for (int k = 0; k < top; ++k) {                          // serial selection; the first chosen logit is the largest
+        int bi = 0;
+        float bv = -INFINITY;
+        for (int e = 0; e < E; ++e)
+          if (s[e] > bv) { bv = s[e]; bi = e; }
+        if (k == 0) first = bv;
+        const float w = expf(bv - first);
+        ids[(size_t)m * top + k] = bi;
+        wts[(size_t)m * top + k] = w;
+        den += w;
+        s[bi] = -INFINITY;                                     // taken
+      }
+      for (int k = 0; k < top; ++k) wts[(size_t)m * top + k] /= den;
+    }
+    return;
+  }
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
   mx = warp_max(mx);
@@ -286,20 +373,36 @@ __device__ __host__ __forceinline__ size_t moe_up_row(int f, int F, int il8) { r
 // ---------------------------------------------------------------------------------------------------------------------------
 // Mixture of experts, row form (few rows, and the 32-bit mode): every (row, chosen expert) streams that expert's matrices.
 //   moe_rows_up_kernel   act[m, k, f] = silu(W_gate[e] h_m)[f] * (W_up[e] h_m)[f],  e = ids[m, k]        one warp per f
-//   moe_rows_down_kernel y[m, d] = sum_k wts[m, k] * (W_down[e_k] act[m, k, :])[d]                       one warp per d
-// w_down: [E][D, F].
+//                        ungated experts (w_gu is then [E][F, D], up rows only): act[m, k, f] = relu(W_up[e] h_m)[f]^2
+//   moe_rows_down_kernel y[m, d] (+)= sum_k wts[m, k] * (W_down[e_k] act[m, k, :])[d]                    one warp per d
+// w_down: [E][D, F].  With `accumulate` the sum is added to what y holds (a shared expert's output).
 // ---------------------------------------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void moe_rows_up_kernel(const T* __restrict__ h, int D, const T* __restrict__ w_gu, int F, int il8, const int* __restrict__ ids, int top,
-                                   T* __restrict__ act) {
+__global__ void moe_rows_up_kernel(const T* __restrict__ h, int D, const T* __restrict__ w_gu, int F, int il8, int gated, const int* __restrict__ ids,
+                                   int top, T* __restrict__ act) {
   extern __shared__ __align__(16) float hs[];                  // the row, fp32
   const int m = blockIdx.x, k = blockIdx.y;
   const int e = ids[(size_t)m * top + k];
   for (int d = threadIdx.x; d < D; d += blockDim.x) hs[d] = ldf(h + (size_t)m * D + d);
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  const T* we = w_gu + (size_t)e * 2 * F * D;
+  const T* we = w_gu + (size_t)e * (gated ? 2 : 1) * F * D;
   const bool vec = D % (16 / sizeof(T)) == 0 && (reinterpret_cast<uintptr_t>(w_gu) & 15) == 0;
+  if (!gated) {                                                // two up rows per round: twice the loads in flight
+    const int step = gridDim.z * nw;
+    for (int f = blockIdx.z * nw + warp; f < F; f += 2 * step) {
+      const int f1 = f + step < F ? f + step : f;
+      float u0, u1;
+      row_dot2(we + (size_t)f * D, we + (size_t)f1 * D, hs, hs, D, lane, vec, u0, u1);
+      if (lane == 0) {
+        u0 = fmaxf(u0, 0.f);
+        u1 = fmaxf(u1, 0.f);
+        stf(act + ((size_t)m * top + k) * F + f, u0 * u0);
+        if (f1 != f) stf(act + ((size_t)m * top + k) * F + f1, u1 * u1);
+      }
+    }
+    return;
+  }
   for (int f = blockIdx.z * nw + warp; f < F; f += gridDim.z * nw) {
     float g, u;
     row_dot2(we + moe_gate_row(f, F, il8) * D, we + moe_up_row(f, F, il8) * D, hs, hs, D, lane, vec, g, u);
@@ -308,7 +411,7 @@ __global__ void moe_rows_up_kernel(const T* __restrict__ h, int D, const T* __re
 }
 template <typename T>
 __global__ void moe_rows_down_kernel(const T* __restrict__ act, int F, const T* __restrict__ w_down, int D, const int* __restrict__ ids,
-                                     const float* __restrict__ wts, int top, float* __restrict__ y) {
+                                     const float* __restrict__ wts, int top, int accumulate, float* __restrict__ y) {
   extern __shared__ __align__(16) float as[];                  // [top][F] fp32
   const int m = blockIdx.x;
   for (int i = threadIdx.x; i < top * F; i += blockDim.x) as[i] = ldf(act + (size_t)m * top * F + i);
@@ -336,7 +439,7 @@ __global__ void moe_rows_down_kernel(const T* __restrict__ act, int F, const T* 
       out = fmaf(wts[(size_t)m * top + k + 1], r1, out);
     }
     if (k < top) out = fmaf(wts[(size_t)m * top + k], row_dot(w_down + ((size_t)ids[(size_t)m * top + k] * D + d) * F, as + k * F, F, lane, vec), out);
-    if (lane == 0) y[(size_t)m * D + d] = out;
+    if (lane == 0) y[(size_t)m * D + d] = accumulate ? y[(size_t)m * D + d] + out : out;
   }
 }
 
@@ -345,7 +448,7 @@ __global__ void moe_rows_down_kernel(const T* __restrict__ act, int F, const T* 
 // run padded to whole 128-row tiles, and two tensor-core products run over the tiles with the expert's matrices chosen per tile.
 //   moe_plan_kernel    (one block)  counts -> padded run starts, tile -> expert map (-1 beyond the last run), cursors reset
 //   moe_scatter_kernel (one warp per pair) takes the pair's place in its expert's run, remembers it, copies the row there
-//   moe_combine_kernel y[m, :] = sum_k wts[m, k] * yg[place[m, k], :]
+//   moe_combine_kernel y[m, :] (+)= sum_k wts[m, k] * yg[place[m, k], :]
 // ints: counts[E], starts[E + 1], cursor[E], then tile_expert[n_tiles].  The order of pairs inside a run depends on scheduling; a
 // pair's result does not (rows of a product are independent).
 // ---------------------------------------------------------------------------------------------------------------------------
@@ -405,12 +508,12 @@ __global__ void moe_scatter_kernel(const T* __restrict__ h, int D, const int* __
   }
 }
 __global__ void moe_combine_kernel(const float* __restrict__ yg, const int* __restrict__ place, const float* __restrict__ wts, int top, int D,
-                                   float* __restrict__ y) {
+                                   int accumulate, float* __restrict__ y) {
   const size_t m = blockIdx.x;
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float acc = 0.f;
     for (int k = 0; k < top; ++k) acc = fmaf(wts[m * top + k], yg[(size_t)place[m * top + k] * D + d], acc);
-    y[m * D + d] = acc;
+    y[m * D + d] = accumulate ? y[m * D + d] + acc : acc;
   }
 }
 

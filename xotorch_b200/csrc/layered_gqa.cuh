@@ -7,14 +7,21 @@
 //   score(i, j) = q_i . k_j * scale                       fp32
 //                 -> cap * tanh(score / cap)              when cap > 0
 //                 -> - r1[a] * ln(1 + r2[a] * (i - j))    when the head has a distance penalty
+//                 -> + rel[a][min(i - j, rel_n - 1)]      when the layer has a learned bias per distance bucket (tabulated per
+//                                                         distance; from rel_n - 1 on every distance is in the last bucket)
 //   visible     : j <= i,  i - j < window (window > 0),  floor(i / chunk) == floor(j / chunk) (chunk > 0; blocks are counted from
 //                 position 0 of the request, whatever portion of it a step brings)
-//   weights     = softmax over the visible keys (fp32), output = sum_j p_j v_j, times sigmoid(gate) per head or per entry.
+//   weights     = softmax over the visible keys (fp32); with a sink the denominator also holds exp(sink[a]), a term that has no
+//                 key, no value, no scale and no bias and counts once; output = sum_j p_j v_j, times sigmoid(gate) per head or
+//                 per entry.
+// Queries may carry a temperature: the query at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1).
 //
-// Kernels: gqa_prepare_kernel (bias, per-head RMS norm, cache append), gqa_attention_kernel + gqa_combine_kernel (one warp per
-// (row, query head); decode, short portions and the 32-bit mode), gqa_flash_kernel (tensor cores, bf16, long portions).
+// Kernels: gqa_prepare_kernel (bias, per-head RMS norm, temperature, cache append), gqa_prepare_row_kernel (the same with ONE norm
+// over the whole query / key projection), gqa_attention_kernel + gqa_combine_kernel (one warp per (row, query head); decode,
+// short portions and the 32-bit mode), gqa_flash_kernel (tensor cores, bf16, long portions).
 #pragma once
 #include "layered_kernels.cuh"
+#include "layered_blocks.cuh"
 
 namespace xl {
 
@@ -23,23 +30,39 @@ struct GqaScore {
   int window, chunk;
   const void* r1;    // per query head, T; NULL = no distance penalty
   const void* r2;
+  const float* rel;  // [H][rel_n] fp32: learned bias per distance, the last entry for every larger distance; NULL = none
+  int rel_n;
+  const void* sink;  // per query head, T; NULL = no sink
 };
 
+// multiplier of the query at position pos (1 when coef == 0)
+__device__ __forceinline__ float gqa_query_temperature(float coef, int every, int pos) {
+  return coef != 0.f ? 1.0f + coef * logf((float)((pos + 1) / every + 1)) : 1.0f;
+}
+// folds a sink into finished softmax statistics: returns the factor for the accumulator, updates the denominator
+__device__ __forceinline__ float gqa_apply_sink(float sink, float mx, float& den) {
+  const float nmx = fmaxf(mx, sink);
+  const float corr = mx == -INFINITY ? 0.f : expf(mx - nmx);
+  den = den * corr + expf(sink - nmx);
+  return corr;
+}
+
 template <typename T>
-__device__ __forceinline__ float gqa_adjust(float dot, const GqaScore& sc, float r1, float r2, int dist) {
+__device__ __forceinline__ float gqa_adjust(float dot, const GqaScore& sc, float r1, float r2, const float* __restrict__ rel_head, int dist) {
   float s = dot * sc.scale;
   if (sc.cap > 0.f) s = sc.cap * tanhf(s / sc.cap);
   if (sc.r1) s -= r1 * log1pf(r2 * (float)dist);
+  if (rel_head) s += rel_head[min(dist, sc.rel_n - 1)];
   return s;
 }
 // the same in the tensor-core prompt kernel: fp32 with the fast exponential and division units (tanh x = (e^2x - 1) / (e^2x + 1))
-__device__ __forceinline__ float gqa_adjust_fast(float dot, const GqaScore& sc, float inv_cap, const float* __restrict__ dist_penalty, int dist) {
+__device__ __forceinline__ float gqa_adjust_fast(float dot, const GqaScore& sc, float inv_cap, const float* __restrict__ dist_bias, int dist) {
   float s = dot * sc.scale;
   if (sc.cap > 0.f) {
     const float t = __expf(2.0f * fminf(fmaxf(s * inv_cap, -15.f), 15.f));
     s = sc.cap * __fdividef(t - 1.0f, t + 1.0f);
   }
-  if (dist_penalty) s -= dist_penalty[dist];                   // r1 * ln(1 + r2 * distance), tabulated per head; the caller's index
+  if (dist_bias) s += dist_bias[dist];                         // learned bias - r1 * ln(1 + r2 * distance), staged per tile; the caller's index
   return s;
 }
 __device__ __forceinline__ bool gqa_visible(int pos, int j, int window, int chunk) {
@@ -57,14 +80,14 @@ __device__ __host__ __forceinline__ int gqa_first_key(int pos0, int window, int 
 // After the input projection: proj[m, :] (fp32) holds q (H * dk) at col_q and, for a layer with keys/values of its own, k (G * dk)
 // at col_k and v (G * dv) at col_v.  Adds the projection biases, RMS-norms every query and key head over dk (weight of size dk
 // shared by the heads; w == NULL: no norm) and stores queries as fp32 [M, H, dk] (+ a bf16 copy for the tensor-core kernel) and
-// keys / values into the row's place of the paged pool.  One warp per (row, head slot): slots 0..H-1 queries, H..H+G-1 keys,
-// H+G..H+2G-1 values.
+// keys / values into the row's place of the paged pool; queries are multiplied by their temperature.  One warp per (row, head
+// slot): slots 0..H-1 queries, H..H+G-1 keys, H+G..H+2G-1 values.
 // ---------------------------------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void gqa_prepare_kernel(const float* __restrict__ proj, int ld, int col_q, int col_k, int col_v, const T* __restrict__ bias,
                                    const T* __restrict__ q_norm, const T* __restrict__ k_norm, float eps, int H, int G, int dk, int dv, int own_kv,
-                                   const int* __restrict__ row_slot, const int* __restrict__ row_pos, Paging pg, T* __restrict__ pool,
-                                   float* __restrict__ qf, bf16* __restrict__ q16, int M) {
+                                   float q_temp_coef, int q_temp_every, const int* __restrict__ row_slot, const int* __restrict__ row_pos, Paging pg,
+                                   T* __restrict__ pool, float* __restrict__ qf, bf16* __restrict__ q16, int M) {
   const int slots = H + (own_kv ? 2 * G : 0);
   const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (idx >= M * slots) return;
@@ -81,7 +104,7 @@ __global__ void gqa_prepare_kernel(const float* __restrict__ proj, int ld, int c
   const T* w = is_q ? q_norm : k_norm;
   float ss = 0.f;
   for (int d = lane; d < dk; d += 32) { const float v = pr[c0 + d] + (bias ? ldf(bias + c0 + d) : 0.f); ss = fmaf(v, v, ss); }
-  const float rs = w ? 1.0f / sqrtf(warp_sum(ss) / (float)dk + eps) : 1.0f;
+  const float rs = (w ? 1.0f / sqrtf(warp_sum(ss) / (float)dk + eps) : 1.0f) * (is_q ? gqa_query_temperature(q_temp_coef, q_temp_every, row_pos[m]) : 1.0f);
   T* kdst = is_q ? nullptr : pool + pg.row(row_slot[m], row_pos[m]) * (size_t)(G * (dk + dv)) + (size_t)hd * dk;
   for (int d = lane; d < dk; d += 32) {
     const float v = (pr[c0 + d] + (bias ? ldf(bias + c0 + d) : 0.f)) * rs * (w ? ldf(w + d) : 1.f);
@@ -92,6 +115,45 @@ __global__ void gqa_prepare_kernel(const float* __restrict__ proj, int ld, int c
       stf(kdst + d, v);
     }
   }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// The same step for layers whose query / key norm runs over the WHOLE projection: q (all H * dk entries of the row, bias added)
+// is divided by its root mean square and multiplied by a weight of that size, and so is k (G * dk entries).  One block per row;
+// two block-wide sums, then every thread writes its share of q (fp32, + bf16 copy), k and v (paged pool).
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void gqa_prepare_row_kernel(const float* __restrict__ proj, int ld, int col_q, int col_k, int col_v, const T* __restrict__ bias,
+                                       const T* __restrict__ q_norm, const T* __restrict__ k_norm, float eps, int H, int G, int dk, int dv, int own_kv,
+                                       float q_temp_coef, int q_temp_every, const int* __restrict__ row_slot, const int* __restrict__ row_pos, Paging pg,
+                                       T* __restrict__ pool, float* __restrict__ qf, bf16* __restrict__ q16) {
+  __shared__ float red[32];
+  const int m = blockIdx.x, nq = H * dk, nk = G * dk, nv = G * dv;
+  const float* pr = proj + (size_t)m * ld;
+  float sq = 0.f, sk = 0.f;
+  for (int c = threadIdx.x; c < nq; c += blockDim.x) { const float v = pr[col_q + c] + (bias ? ldf(bias + col_q + c) : 0.f); sq = fmaf(v, v, sq); }
+  if (own_kv)
+    for (int c = threadIdx.x; c < nk; c += blockDim.x) { const float v = pr[col_k + c] + (bias ? ldf(bias + col_k + c) : 0.f); sk = fmaf(v, v, sk); }
+  const float rq = 1.0f / sqrtf(block_sum(sq, red) / (float)nq + eps) * gqa_query_temperature(q_temp_coef, q_temp_every, row_pos[m]);
+  for (int c = threadIdx.x; c < nq; c += blockDim.x) {
+    const float v = (pr[col_q + c] + (bias ? ldf(bias + col_q + c) : 0.f)) * rq * ldf(q_norm + c);
+    qf[(size_t)m * nq + c] = v;
+    if (q16) q16[(size_t)m * nq + c] = __float2bfloat16_rn(v);
+  }
+  if (!own_kv) return;                                         // block-uniform
+  const float rk = 1.0f / sqrtf(block_sum(sk, red) / (float)nk + eps);
+  T* dst = pool + pg.row(row_slot[m], row_pos[m]) * (size_t)(nk + nv);
+  for (int c = threadIdx.x; c < nk; c += blockDim.x) stf(dst + c, (pr[col_k + c] + (bias ? ldf(bias + col_k + c) : 0.f)) * rk * ldf(k_norm + c));
+  for (int c = threadIdx.x; c < nv; c += blockDim.x) stf(dst + nk + c, pr[col_v + c] + (bias ? ldf(bias + col_v + c) : 0.f));
+}
+
+// table[a][d] = rel[bucket_of[d], a] for d < n: the learned bias of head a at distance d (rel is [buckets, H] as stored)
+template <typename T>
+__global__ void gqa_rel_table_kernel(const T* __restrict__ rel, const int* __restrict__ bucket_of, int H, int n, float* __restrict__ table) {
+  const size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  if (i >= (size_t)H * n) return;
+  const int a = (int)(i / n), d = (int)(i % n);
+  table[i] = ldf(rel + (size_t)bucket_of[d] * H + a);
 }
 
 // how the mixer output is gated: 0 none, 1 sigmoid(gate[m, col0 + head]), 2 sigmoid(gate[m, col0 + head * dv + d])
@@ -131,6 +193,7 @@ __global__ void gqa_attention_kernel(const float* __restrict__ qf, const T* __re
     for (int d = lane; d < dk; d += 32) q[d] = src[d];
   }
   const float r1 = sc.r1 ? ldf(static_cast<const T*>(sc.r1) + h) : 0.f, r2 = sc.r1 ? ldf(static_cast<const T*>(sc.r2) + h) : 0.f;
+  const float* rel_head = sc.rel ? sc.rel + (size_t)h * sc.rel_n : nullptr;
   int last = it.pos0 + it.n_rows - 1;
   int first = gqa_first_key(it.pos0, sc.window, sc.chunk);
   if (gridDim.z > 1) {
@@ -162,7 +225,7 @@ __global__ void gqa_attention_kernel(const float* __restrict__ qf, const T* __re
     float s = 0.f;
     const float* kr = ktile + lane * WS;
     for (int d = 0; d < dk; ++d) s = fmaf(q[d], kr[d], s);
-    s = vis ? gqa_adjust<T>(s, sc, r1, r2, pos - j) : -INFINITY;
+    s = vis ? gqa_adjust<T>(s, sc, r1, r2, rel_head, pos - j) : -INFINITY;
     const float tmax = warp_max(s);
     if (tmax == -INFINITY) continue;                           // warp-uniform
     const float nmx = fmaxf(mx, tmax);
@@ -194,7 +257,8 @@ __global__ void gqa_attention_kernel(const float* __restrict__ qf, const T* __re
     }
     return;
   }
-  const float inv = 1.0f / den;
+  const float corr = sc.sink ? gqa_apply_sink(ldf(static_cast<const T*>(sc.sink) + h), mx, den) : 1.0f;
+  const float inv = corr / den;
   T* o = out + (size_t)m * H * dv + (size_t)h * dv;
 #pragma unroll
   for (int a = 0; a < NACC; ++a) {
@@ -203,9 +267,10 @@ __global__ void gqa_attention_kernel(const float* __restrict__ qf, const T* __re
   }
 }
 
-// merges the key runs: one warp per (row, query head) of the listed items; at most 32 runs
+// merges the key runs: one warp per (row, query head) of the listed items; at most 32 runs.  A sink (per head, may be NULL) joins
+// here, once, like a run that holds the weight exp(sink) and no values.
 template <typename T>
-__global__ void gqa_combine_kernel(const float* __restrict__ part, const Item* __restrict__ items, int H, int dv, int splits,
+__global__ void gqa_combine_kernel(const float* __restrict__ part, const Item* __restrict__ items, int H, int dv, int splits, const T* __restrict__ sink,
                                    const float* __restrict__ gate, int gate_mode, int gate_ld, int gate_col0, T* __restrict__ out) {
   const Item it = items[blockIdx.x];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
@@ -214,9 +279,10 @@ __global__ void gqa_combine_kernel(const float* __restrict__ part, const Item* _
   const int m = it.row0 + pair / H, h = pair % H;
   const float* src = part + ((size_t)m * H + h) * splits * (size_t)(2 + dv);
   const float mz = lane < splits ? src[(size_t)lane * (2 + dv)] : -INFINITY;
-  const float mx = warp_max(mz);
+  const float sk = sink ? ldf(sink + h) : -INFINITY;
+  const float mx = fmaxf(warp_max(mz), sk);
   const float wz = mz == -INFINITY ? 0.f : expf(mz - mx);
-  const float den = warp_sum(lane < splits ? src[(size_t)lane * (2 + dv) + 1] * wz : 0.f);
+  const float den = warp_sum(lane < splits ? src[(size_t)lane * (2 + dv) + 1] * wz : 0.f) + (sink ? expf(sk - mx) : 0.f);
   const float inv = 1.0f / den;
   for (int d0 = 0; d0 < dv; d0 += 32) {
     const int d = d0 + lane;
@@ -261,7 +327,7 @@ gqa_flash_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ pool, Pa
                  bf16* __restrict__ out) {
   extern __shared__ __align__(16) uint8_t gsm[];
   __shared__ size_t krow[2][64];                    // pool rows of the keys of the tile in flight / in use
-  __shared__ float dpen[2][128];                    // distance penalties a (64 rows x 64 keys) tile can meet: distance = dbase + index
+  __shared__ float dpen[2][128];                    // distance terms (learned bias - penalty) a (64 rows x 64 keys) tile can meet: distance = dbase + index
   const GqaTile tl = tiles[gridDim.x - 1 - blockIdx.x];   // later tiles of a request see more keys: the long ones start first
   const int h = blockIdx.y, g = h / (H / G);
   const int DQP = (dk + 15) & ~15, QS = DQP + 8;
@@ -276,6 +342,8 @@ gqa_flash_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ pool, Pa
   const int qc = DQP / 8;
   const size_t rowlen = (size_t)G * (dk + dv);
   const float* dtab = dist_table ? dist_table + (size_t)h * dist_n : nullptr;
+  const float* rtab = sc.rel ? sc.rel + (size_t)h * sc.rel_n : nullptr;
+  const bool dist_terms = dtab || rtab;
 
   // the page walk is done once per key (64 threads), then every thread copies 16-byte pieces from the rows it names
   auto locate = [&](int j0, int bsel) {
@@ -320,9 +388,12 @@ gqa_flash_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ pool, Pa
   issue(first, 0);
   for (int it = 0; it < ntile; ++it) {
     const int j0 = first + it * 64, bsel = it & 1;
-    if (dtab) {                                      // distances pos0 - (j0 + 63) + index; negative ones belong to keys after the row (masked)
+    if (dist_terms) {                                // distances pos0 - (j0 + 63) + index; negative ones belong to keys after the row (masked)
       const int d = tl.pos0 - j0 - 63 + (int)threadIdx.x;
-      dpen[bsel][threadIdx.x] = d >= 0 && d < dist_n ? dtab[d] : 0.f;
+      float b = 0.f;
+      if (dtab && d >= 0 && d < dist_n) b = -dtab[d];
+      if (rtab && d >= 0) b += rtab[min(d, sc.rel_n - 1)];
+      dpen[bsel][threadIdx.x] = b;
     }
     if (it + 1 < ntile) {
       issue(j0 + 64, bsel ^ 1);
@@ -355,7 +426,7 @@ gqa_flash_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ pool, Pa
       for (int x = 0; x < 4; ++x) {
         const int j = j0 + n * 8 + 2 * t + (x & 1), pos = (x < 2) ? pos_lo : pos_hi;
         const bool vis = j <= last && j <= pos && j >= vis_lo[x >> 1];
-        s[n][x] = vis ? gqa_adjust_fast(s[n][x], sc, inv_cap, dtab ? dpen[bsel] : nullptr, (pos - tl.pos0) - (j - j0) + 63) : -INFINITY;
+        s[n][x] = vis ? gqa_adjust_fast(s[n][x], sc, inv_cap, dist_terms ? dpen[bsel] : nullptr, (pos - tl.pos0) - (j - j0) + 63) : -INFINITY;
         tmax[x >> 1] = fmaxf(tmax[x >> 1], s[n][x]);
       }
     float corr[2], nmx[2];
@@ -411,7 +482,8 @@ gqa_flash_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ pool, Pa
     const int qi = warp * 16 + gq + r * 8;
     if (qi >= tl.n_rows) continue;
     const size_t m = tl.row0 + qi;
-    const float inv = 1.0f / den[r];
+    const float corr = sc.sink ? gqa_apply_sink(__bfloat162float(static_cast<const bf16*>(sc.sink)[h]), mx[r], den[r]) : 1.0f;
+    const float inv = corr / den[r];
     bf16* dst = out + m * ((size_t)H * dv) + (size_t)h * dv;
 #pragma unroll
     for (int i = 0; i < DVT; ++i) {

@@ -688,15 +688,21 @@ gemv_rows_kernel(const TA* __restrict__ A, long lda, long a_batch, const TB* __r
   }
 }
 
-// lowest-index argmax of every row of an fp32 matrix (greedy sampling on the device)
-__global__ void argmax_rows_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
+// finishes the logits of every row in place — l <- l * scale, then l <- cap * tanh(l / cap) when cap > 0 — and takes the
+// lowest-index argmax of the row (greedy sampling on the device)
+__global__ void argmax_rows_kernel(float* __restrict__ logits, int V, float scale, float cap, int* __restrict__ out) {
   __shared__ float bv[32];
   __shared__ int bi[32];
-  const float* r = logits + (size_t)blockIdx.x * V;
+  float* r = logits + (size_t)blockIdx.x * V;
   float best = -INFINITY;
   int idx = 0x7fffffff;
   for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = r[i];
+    float v = r[i];
+    if (scale != 1.0f || cap > 0.f) {
+      v *= scale;
+      if (cap > 0.f) v = cap * tanhf(v / cap);
+      r[i] = v;
+    }
     if (v > best || (v == best && i < idx)) { best = v; idx = i; }
   }
 #pragma unroll

@@ -55,6 +55,16 @@ class LayerSpec:
   groups: int = 0
   groups_keep: int = 0
   softcap: float = 0.0
+  out_bias: int = 0
+  sink: int = 0
+  rel_buckets: int = 0
+  rel_max: float = 0.0
+  q_temp_coef: float = 0.0
+  q_temp_every: int = 0
+  expert_act: int = _lib.LM_EXPERT_SILU_GATED
+  router_kind: int = _lib.LM_ROUTER_SOFTMAX_ALL
+  router_bias: int = 0
+  shared_ff: int = 0
 
   def to_c(self) -> LmLayer:
     c = LmLayer()
@@ -169,7 +179,58 @@ def bufulorn_globals(config: dict) -> dict:
               block=_lib.LM_BLOCK_POST_LN, max_positions=int(config["max_positions"]))
 
 
-LAYERED_FAMILIES = {"Zokuvik": (zokuvik_layers, zokuvik_globals), "Bufulorn": (bufulorn_layers, bufulorn_globals)}
+# ---- the Tunavik family ------------------------------------------------------------------------------------------------------
+# config.json: {"architecture": "Tunavik", "width", "vocab", "norm": {"eps"}, "logit_scale", "logit_softcap", "layers": [{"type", "mixer", "mlp"}]}
+# A layer is x += rms(mixer(x)) * (1 + w), x += rms(ff(x)) * (1 + w); a sine/cosine position vector (base 10000) is added to the
+# embedding and the sum is normed the same way (embed.norm); the logits are scaled and soft-capped.
+#   type "attention"  grouped-query attention (mixer: heads, kv_heads, dim, vdim, scale, bias_max, q_temp {coef, every}, kv_from):
+#                     biased q / k / v / o projections, ONE RMS norm over the whole query (key) projection, no rotation, query
+#                     temperature by position, learned bias per logarithmic distance bucket (table l<i>.mix.rel, whose first
+#                     dimension is the number of buckets), one sink logit per head in the softmax denominator
+#   mlp.kind "moe"    relu^2 experts without biases (mlp.expert.ff), router with bias: the `top` largest logits, softmax over them
+#                     (mlp.router {experts, top}); optional shared expert of the same form (mlp.shared.ff)
+TUNAVIK_SINUSOID_BASE = 10000.0
+
+
+def _tunavik_ff(i: int, mlp) -> dict:
+  if mlp is None:
+    return dict(ff=0, ff_kind=_lib.LM_FF_MOE, experts=0)
+  kind = mlp.get("kind")
+  if kind != "moe":
+    raise ValueError(f"layer {i}: feed-forward kind {kind!r} is not implemented (moe)")
+  r = mlp["router"]
+  shared = mlp.get("shared") or {}
+  return dict(ff=0, ff_kind=_lib.LM_FF_MOE, experts=int(r["experts"]), top=int(r["top"]), expert_ff=int(mlp["expert"]["ff"]),
+              expert_act=_lib.LM_EXPERT_RELU2, router_kind=_lib.LM_ROUTER_TOPK_SOFTMAX, router_bias=1, shared_ff=int(shared.get("ff", 0)))
+
+
+def tunavik_layers(config: dict, shapes: Dict[str, Tuple[int, ...]]) -> List[LayerSpec]:
+  out = []
+  for i, layer in enumerate(config["layers"]):
+    kind, m = layer["type"], layer["mixer"]
+    if kind != "attention":
+      raise ValueError(f"layer {i}: mixer type {kind!r} is not implemented")
+    rel = shapes.get(f"l{i}.mix.rel")
+    if rel is None or len(rel) != 2:
+      raise ValueError(f"layer {i}: tensor l{i}.mix.rel (whose first dimension is the number of distance buckets) is missing")
+    temp = m.get("q_temp") or {}
+    src = m.get("kv_from")
+    out.append(LayerSpec(
+      mixer=_lib.LM_MIX_ATTENTION, heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=int(m["dim"]), vdim=int(m["vdim"]),
+      scale=float(m["scale"]), kv_from=-1 if src is None else int(src), qk_norm=_lib.LM_QKNORM_ROW, proj_bias=1, out_bias=1, sink=1,
+      rel_buckets=int(rel[0]), rel_max=float(m["bias_max"]), q_temp_coef=float(temp.get("coef", 0.0)), q_temp_every=int(temp.get("every", 1)),
+      **_tunavik_ff(i, layer.get("mlp"))))
+  return out
+
+
+def tunavik_globals(config: dict) -> dict:
+  return dict(width=int(config["width"]), vocab=int(config["vocab"]), norm_groups=1, norm_eps=float(config["norm"]["eps"]),
+              block=_lib.LM_BLOCK_POST_RMS, pos_sinusoid=1, sinusoid_base=TUNAVIK_SINUSOID_BASE, embed_norm=1,
+              logit_scale=float(config.get("logit_scale", 1.0)), logit_softcap=float(config.get("logit_softcap") or 0.0))
+
+
+LAYERED_FAMILIES = {"Zokuvik": (zokuvik_layers, zokuvik_globals), "Bufulorn": (bufulorn_layers, bufulorn_globals),
+                    "Tunavik": (tunavik_layers, tunavik_globals)}
 
 
 class LayeredShard:
@@ -224,6 +285,9 @@ class LayeredShard:
     cfg.width, cfg.vocab, cfg.norm_groups = self.globals["width"], self.globals["vocab"], self.globals["norm_groups"]
     cfg.norm_eps = self.globals["norm_eps"]
     cfg.block, cfg.max_positions = self.globals.get("block", _lib.LM_BLOCK_GROUP_RMS), self.globals.get("max_positions", 0)
+    cfg.pos_sinusoid, cfg.sinusoid_base = self.globals.get("pos_sinusoid", 0), self.globals.get("sinusoid_base", 0.0)
+    cfg.embed_norm = self.globals.get("embed_norm", 0)
+    cfg.logit_scale, cfg.logit_softcap = self.globals.get("logit_scale", 1.0), self.globals.get("logit_softcap", 0.0)
     cfg.dtype = _lib.LM_DTYPE_F32 if self.dtype == "float32" else _lib.LM_DTYPE_BF16
     arr = (LmLayer * len(specs))(*[s.to_c() for s in specs])
     h = C.c_void_p()
