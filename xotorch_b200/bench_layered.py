@@ -6,6 +6,10 @@ per cent) weight bytes.  One JSON line per size; nothing here touches bench.py's
 values, dense and mixture-of-experts feed-forwards) beside the closest existing family on the same engine, a Zokuvik model of
 the same width and depth whose feed-forward size is chosen so that the weight bytes match.
 
+`--layered-family tunavik`: the same for Tunavik-shaped models (grouped-query attention with learned distance biases, sinks and
+shared keys / values; relu^2 experts with a shared expert) beside the closest existing family on the same engine, a Bufulorn
+model of attention layers only with the same heads, layer pattern and (to a few per cent) weight bytes.
+
 Timing: every number is the device time of the step(s) (CUDA events on the engine's stream, `last_step_ms` / the ring's own
 timer), after warm-up; the weights of every size are larger than L2 from `medium` on, and each prompt step streams all of them.
 Roofline denominators come from MEASURED_PEAKS.json (fallback: the profiling recipe's numbers)."""
@@ -73,6 +77,49 @@ def bufulorn_config(s: dict, b: dict, context: int):
   cfg = {"architecture": "Bufulorn", "width": s["width"], "vocab": s["vocab"], "max_positions": context, "norm": {"eps": 1e-5}, "layers": layers}
   n_moe = sum(1 for l in layers if l["mlp"]["kind"] == "moe")
   idle = n_moe * (EXPERTS - TOP) * 3 * (s["ff"] // 4) * s["width"] * 2          # bytes of the experts one token does not use
+  return cfg, idle
+
+
+# Tunavik shapes at the same widths: attention heads as the Bufulorn attention layers, per repeat [owner, owner, borrower of the
+# second owner], every layer with 16 relu^2 experts (4 per token) and a shared expert of an expert's size; 32 distance buckets up
+# to distance 2048, query temperature stepping every 1024 positions.  The Bufulorn model beside it has the same pattern with gated
+# experts; the Tunavik experts' inner size is chosen so that (16 + 1) two-matrix experts weigh what 16 three-matrix experts do.
+REL_BUCKETS, REL_FAR, TEMP_EVERY = 32, 2048, 1024
+
+
+def tunavik_config(s: dict, b: dict):
+  fb = s["ff"] // 4
+  ft = max(64, int(EXPERTS * 3 * fb / ((EXPERTS + 1) * 2)) // 64 * 64)
+  moe = {"kind": "moe", "router": {"experts": EXPERTS, "top": TOP}, "expert": {"ff": ft}, "shared": {"ff": ft}}
+  def att(src):
+    m = {"heads": b["heads"], "kv_heads": b["kv_heads"], "dim": b["dim"], "vdim": b["vdim"], "scale": float(b["dim"] ** -0.5), "bias_max": REL_FAR,
+         "q_temp": {"coef": 0.5, "every": TEMP_EVERY}}
+    if src is not None:
+      m["kv_from"] = src
+    return {"type": "attention", "mixer": m, "mlp": moe}
+  layers = []
+  for r in range(s["repeats"]):
+    layers += [att(None), att(None), att(3 * r + 1)]
+  cfg = {"architecture": "Tunavik", "width": s["width"], "vocab": s["vocab"], "norm": {"eps": 1e-5}, "logit_scale": 0.5, "logit_softcap": 30.0, "layers": layers}
+  shapes = {f"l{i}.mix.rel": (REL_BUCKETS, b["heads"]) for i in range(len(layers))}
+  idle = len(layers) * (EXPERTS - TOP) * 2 * ft * s["width"] * 2
+  return cfg, shapes, idle, ft
+
+
+def bufulorn_attention_config(s: dict, b: dict, context: int):
+  """Bufulorn layers of the same pattern: causal attention without blocks, 16 gated experts (4 per token, no groups)"""
+  fb = s["ff"] // 4
+  moe = {"kind": "moe", "router": {"experts": EXPERTS, "top": TOP}, "expert": {"ff": fb}}
+  def att(src):
+    m = {"heads": b["heads"], "kv_heads": b["kv_heads"], "dim": b["dim"], "vdim": b["vdim"], "scale": float(b["dim"] ** -0.5), "softcap": 30.0}
+    if src is not None:
+      m["kv_from"] = src
+    return {"type": "attention", "mixer": m, "mlp": moe}
+  layers = []
+  for r in range(s["repeats"]):
+    layers += [att(None), att(None), att(3 * r + 1)]
+  cfg = {"architecture": "Bufulorn", "width": s["width"], "vocab": s["vocab"], "max_positions": context, "norm": {"eps": 1e-5}, "layers": layers}
+  idle = len(layers) * (EXPERTS - TOP) * 3 * fb * s["width"] * 2
   return cfg, idle
 
 
@@ -218,12 +265,34 @@ def run_bufulorn(args, sizes, prompts, hbm, tf, src) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_tunavik(args, sizes, prompts, hbm, tf, src) -> None:
+  for name in sizes:
+    s, b = SIZES[name], BUFULORN[name]
+    warm = max(3, args.warmup)
+    context = max(max(prompts), 1024 + 9 * (args.steps * 8 + warm)) + 64
+    cfg, shapes, idle, ft = tunavik_config(s, b)
+    tu = layered_numbers(s, prompts, decode_ctx=1024, decode_batches=[1, 8], steps=args.steps, warmup=warm, cfg=cfg, shapes=shapes, idle_bytes=idle)
+    bcfg, bidle = bufulorn_attention_config(s, b, context)
+    bu = layered_numbers(s, prompts, decode_ctx=1024, decode_batches=[1, 8], steps=args.steps, warmup=warm, cfg=bcfg, idle_bytes=bidle)
+    line = {"bench": "layered", "family": "tunavik", "size": name, "dtype": "bf16", "data": "synthetic", "shape": dict(s, **b, expert_ff=ft), "tunavik": tu,
+            "idle_expert_bytes": idle, "bufulorn_same_size": bu, "bufulorn_idle_expert_bytes": bidle,
+            "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src},
+            "frac_of_peak": {
+              "tunavik_decode1_hbm": round(tu["decode"]["1"]["gbs_weights_device"] / hbm, 3),
+              "bufulorn_decode1_hbm": round(bu["decode"]["1"]["gbs_weights_device"] / hbm, 3),
+              **{f"tunavik_prefill{n}_tensor": round(tu["prefill"][str(n)]["tflops_weights"] / tf, 3) for n in prompts},
+              **{f"bufulorn_prefill{n}_tensor": round(bu["prefill"][str(n)]["tflops_weights"] / tf, 3) for n in prompts}}}
+    print(json.dumps(line), flush=True)
+
+
 def run(args) -> None:
   hbm, tf, src = peaks()
   sizes = [x for x in (args.layered_sizes or "small,medium,large").split(",") if x]
   prompts = [int(x) for x in (args.layered_prompts or "1024,4096").split(",")]
   if (getattr(args, "layered_family", "") or "zokuvik") == "bufulorn":
     return run_bufulorn(args, sizes, prompts, hbm, tf, src)
+  if getattr(args, "layered_family", "") == "tunavik":
+    return run_tunavik(args, sizes, prompts, hbm, tf, src)
   for name in sizes:
     s = SIZES[name]
     z = layered_numbers(s, prompts, decode_ctx=1024, decode_batches=[1, 8], steps=args.steps, warmup=max(3, args.warmup))

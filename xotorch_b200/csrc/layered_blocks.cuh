@@ -278,6 +278,35 @@ __device__ __forceinline__ void row_dot4(const T* const (&w)[4], const float* co
   for (int i = 0; i < 4; ++i) r[i] = warp_sum(a[i]);
 }
 
+// four rows of x against two sets of four weight rows (wa[i] . x[i] and wb[i] . x[i]): eight loads in flight per lane
+template <typename T>
+__device__ __forceinline__ void row_dot4x2(const T* const (&wa)[4], const T* const (&wb)[4], const float* const (&x)[4], int n, int lane, bool vec,
+                                           float (&ra)[4], float (&rb)[4]) {
+  constexpr int VEC = 16 / sizeof(T);
+  float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
+  if (vec) {
+    for (int k = lane * VEC; k < n; k += 32 * VEC) {
+      uint4 p[4], q[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { p[i] = *reinterpret_cast<const uint4*>(wa[i] + k); q[i] = *reinterpret_cast<const uint4*>(wb[i] + k); }
+#pragma unroll
+      for (int v = 0; v < VEC; ++v)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float xv = x[i][k + v];
+          a[i] = fmaf(ldf(reinterpret_cast<const T*>(&p[i]) + v), xv, a[i]);
+          b[i] = fmaf(ldf(reinterpret_cast<const T*>(&q[i]) + v), xv, b[i]);
+        }
+    }
+  } else {
+    for (int k = lane; k < n; k += 32)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { a[i] = fmaf(ldf(wa[i] + k), x[i][k], a[i]); b[i] = fmaf(ldf(wb[i] + k), x[i][k], b[i]); }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { ra[i] = warp_sum(a[i]); rb[i] = warp_sum(b[i]); }
+}
+
 // ---------------------------------------------------------------------------------------------------------------------------
 // Mixture of experts, router: logits z = W_r h (+ bias) in fp32 (h in T).
 //   kind 0: scores s = softmax(z) over all E experts; experts form `groups` equal groups of neighbours, a group's score is its best
@@ -388,17 +417,19 @@ __global__ void moe_rows_up_kernel(const T* __restrict__ h, int D, const T* __re
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const T* we = w_gu + (size_t)e * (gated ? 2 : 1) * F * D;
   const bool vec = D % (16 / sizeof(T)) == 0 && (reinterpret_cast<uintptr_t>(w_gu) & 15) == 0;
-  if (!gated) {                                                // two up rows per round: twice the loads in flight
+  if (!gated) {                                                // four up rows per round: four loads in flight per lane
     const int step = gridDim.z * nw;
-    for (int f = blockIdx.z * nw + warp; f < F; f += 2 * step) {
-      const int f1 = f + step < F ? f + step : f;
-      float u0, u1;
-      row_dot2(we + (size_t)f * D, we + (size_t)f1 * D, hs, hs, D, lane, vec, u0, u1);
+    for (int f = blockIdx.z * nw + warp; f < F; f += 4 * step) {
+      const T* w4[4];
+      const float* x4[4] = {hs, hs, hs, hs};
+      float u[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) w4[i] = we + (size_t)(f + i * step < F ? f + i * step : f) * D;   // past the end: row f again, not stored
+      row_dot4(w4, x4, D, lane, vec, u);
       if (lane == 0) {
-        u0 = fmaxf(u0, 0.f);
-        u1 = fmaxf(u1, 0.f);
-        stf(act + ((size_t)m * top + k) * F + f, u0 * u0);
-        if (f1 != f) stf(act + ((size_t)m * top + k) * F + f1, u1 * u1);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (f + i * step < F) { const float r = fmaxf(u[i], 0.f); stf(act + ((size_t)m * top + k) * F + f + i * step, r * r); }
       }
     }
     return;
@@ -418,28 +449,52 @@ __global__ void moe_rows_down_kernel(const T* __restrict__ act, int F, const T* 
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const bool vec = F % (16 / sizeof(T)) == 0 && (reinterpret_cast<uintptr_t>(w_down) & 15) == 0;
-  for (int d = blockIdx.y * nw + warp; d < D; d += gridDim.y * nw) {
-    float out = 0.f;
+  // two output entries per warp and round (d and d + dstep), the experts of a row four by four, then two by two, in their order:
+  // eight weight rows in flight per lane
+  const int dstep = gridDim.y * nw;
+  for (int d = blockIdx.y * nw + warp; d < D; d += 2 * dstep) {
+    const bool two = d + dstep < D;
+    const int d2 = two ? d + dstep : d;                // past the end: entry d again, not stored
+    float out = 0.f, out2 = 0.f;
     int k = 0;
-    for (; k + 3 < top; k += 4) {                      // the experts of a row four by four, then two by two, in their order
+    for (; k + 3 < top; k += 4) {
       const T* w4[4];
+      const T* v4[4];
       const float* x4[4];
-      float r4[4];
+      float r4[4], s4[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) { w4[i] = w_down + ((size_t)ids[(size_t)m * top + k + i] * D + d) * F; x4[i] = as + (k + i) * F; }
-      row_dot4(w4, x4, F, lane, vec, r4);
+      for (int i = 0; i < 4; ++i) {
+        const size_t ex = (size_t)ids[(size_t)m * top + k + i] * D;
+        w4[i] = w_down + (ex + d) * F;
+        v4[i] = w_down + (ex + d2) * F;
+        x4[i] = as + (k + i) * F;
+      }
+      row_dot4x2(w4, v4, x4, F, lane, vec, r4, s4);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) out = fmaf(wts[(size_t)m * top + k + i], r4[i], out);
+      for (int i = 0; i < 4; ++i) { out = fmaf(wts[(size_t)m * top + k + i], r4[i], out); out2 = fmaf(wts[(size_t)m * top + k + i], s4[i], out2); }
     }
     for (; k + 1 < top; k += 2) {
-      float r0, r1;
-      row_dot2(w_down + ((size_t)ids[(size_t)m * top + k] * D + d) * F, w_down + ((size_t)ids[(size_t)m * top + k + 1] * D + d) * F, as + k * F,
-               as + (k + 1) * F, F, lane, vec, r0, r1);
-      out = fmaf(wts[(size_t)m * top + k], r0, out);
-      out = fmaf(wts[(size_t)m * top + k + 1], r1, out);
+      const size_t e0 = (size_t)ids[(size_t)m * top + k] * D, e1 = (size_t)ids[(size_t)m * top + k + 1] * D;
+      const T* w4[4] = {w_down + (e0 + d) * F, w_down + (e1 + d) * F, w_down + (e0 + d2) * F, w_down + (e1 + d2) * F};
+      const float* x4[4] = {as + k * F, as + (k + 1) * F, as + k * F, as + (k + 1) * F};
+      float r4[4];
+      row_dot4(w4, x4, F, lane, vec, r4);
+      out = fmaf(wts[(size_t)m * top + k], r4[0], out);
+      out = fmaf(wts[(size_t)m * top + k + 1], r4[1], out);
+      out2 = fmaf(wts[(size_t)m * top + k], r4[2], out2);
+      out2 = fmaf(wts[(size_t)m * top + k + 1], r4[3], out2);
     }
-    if (k < top) out = fmaf(wts[(size_t)m * top + k], row_dot(w_down + ((size_t)ids[(size_t)m * top + k] * D + d) * F, as + k * F, F, lane, vec), out);
-    if (lane == 0) y[(size_t)m * D + d] = accumulate ? y[(size_t)m * D + d] + out : out;
+    if (k < top) {
+      const size_t ex = (size_t)ids[(size_t)m * top + k] * D;
+      float r0, r1;
+      row_dot2(w_down + (ex + d) * F, w_down + (ex + d2) * F, as + k * F, as + k * F, F, lane, vec, r0, r1);
+      out = fmaf(wts[(size_t)m * top + k], r0, out);
+      out2 = fmaf(wts[(size_t)m * top + k], r1, out2);
+    }
+    if (lane == 0) {
+      y[(size_t)m * D + d] = accumulate ? y[(size_t)m * D + d] + out : out;
+      if (two) y[(size_t)m * D + d2] = accumulate ? y[(size_t)m * D + d2] + out2 : out2;
+    }
   }
 }
 
