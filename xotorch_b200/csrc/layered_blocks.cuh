@@ -278,24 +278,35 @@ __device__ __forceinline__ void row_dot4(const T* const (&w)[4], const float* co
   for (int i = 0; i < 4; ++i) r[i] = warp_sum(a[i]);
 }
 
-// four rows of x against two sets of four weight rows (wa[i] . x[i] and wb[i] . x[i]): eight loads in flight per lane
+// four rows of x against two sets of four weight rows (wa[i] . x[i] and wb[i] . x[i])
 template <typename T>
 __device__ __forceinline__ void row_dot4x2(const T* const (&wa)[4], const T* const (&wb)[4], const float* const (&x)[4], int n, int lane, bool vec,
                                            float (&ra)[4], float (&rb)[4]) {
   constexpr int VEC = 16 / sizeof(T);
   float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
   if (vec) {
-    for (int k = lane * VEC; k < n; k += 32 * VEC) {
-      uint4 p[4], q[4];
+    for (int k = lane * VEC; k < n; k += 64 * VEC) {           // two pieces of every row per round: sixteen loads in flight per lane
+      const int k2 = k + 32 * VEC;
+      const bool more = k2 < n;
+      const int kk = more ? k2 : k;                            // past the end the weights read as zero; the index stays inside x
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      uint4 p[4], q[4], p2[4], q2[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) { p[i] = *reinterpret_cast<const uint4*>(wa[i] + k); q[i] = *reinterpret_cast<const uint4*>(wb[i] + k); }
+      for (int i = 0; i < 4; ++i) {
+        p[i] = *reinterpret_cast<const uint4*>(wa[i] + k);
+        q[i] = *reinterpret_cast<const uint4*>(wb[i] + k);
+        p2[i] = more ? *reinterpret_cast<const uint4*>(wa[i] + k2) : z;
+        q2[i] = more ? *reinterpret_cast<const uint4*>(wb[i] + k2) : z;
+      }
 #pragma unroll
       for (int v = 0; v < VEC; ++v)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float xv = x[i][k + v];
+          const float xv = x[i][k + v], xw = x[i][kk + v];
           a[i] = fmaf(ldf(reinterpret_cast<const T*>(&p[i]) + v), xv, a[i]);
           b[i] = fmaf(ldf(reinterpret_cast<const T*>(&q[i]) + v), xv, b[i]);
+          a[i] = fmaf(ldf(reinterpret_cast<const T*>(&p2[i]) + v), xw, a[i]);
+          b[i] = fmaf(ldf(reinterpret_cast<const T*>(&q2[i]) + v), xw, b[i]);
         }
     }
   } else {

@@ -287,9 +287,11 @@ __global__ void gqa_combine_kernel(const float* __restrict__ part, const Item* _
   for (int d0 = 0; d0 < dv; d0 += 32) {
     const int d = d0 + lane;
     float a = 0.f;
-    for (int z = 0; z < splits; ++z) {
-      const float w = __shfl_sync(0xffffffffu, wz, z);
-      if (w != 0.f && d < dv) a = fmaf(src[(size_t)z * (2 + dv) + 2 + d], w, a);
+#pragma unroll 8
+    for (int z = 0; z < splits; ++z) {                         // loads without a branch, so that several are in flight: a run
+      const float w = __shfl_sync(0xffffffffu, wz, z);         // that saw no key has parked zeros and weighs zero
+      const float v = d < dv ? src[(size_t)z * (2 + dv) + 2 + d] : 0.f;
+      a = fmaf(v, w, a);
     }
     if (d < dv) stf(out + (size_t)m * H * dv + (size_t)h * dv + d, a * inv * gqa_gate(gate, gate_mode, m, gate_ld, gate_col0, h, dv, d));
   }
