@@ -272,6 +272,8 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
       REQUIRE(s.out_gate >= 0 && s.out_gate <= 2, "layer %d: unknown output gate %d", li, s.out_gate);
       REQUIRE(s.qk_norm >= XOTB200_LM_QKNORM_NONE && s.qk_norm <= XOTB200_LM_QKNORM_ROW, "layer %d: unknown query/key norm %d", li, s.qk_norm);
       REQUIRE(!s.out_bias || post_ln || post_rms, "layer %d: a bias of the output projection is added by the closing norm of the post-norm block forms only", li);
+      REQUIRE(s.qk_norm != XOTB200_LM_QKNORM_ROW || (size_t)(H + G) * dk * 4 <= 200 * 1024,
+              "layer %d: a query/key norm over the whole projection holds the row in shared memory: (heads + kv_heads) * dim <= 51200", li);
       REQUIRE(s.q_temp_coef == 0.f || s.q_temp_every >= 1, "layer %d: query temperature every %d positions", li, s.q_temp_every);
       REQUIRE(s.rel_buckets == 0 || (s.rel_buckets >= 2 && s.rel_buckets <= 65536 && s.rel_max > (float)(s.rel_buckets / 2) && s.rel_max <= 4194304.f),
               "layer %d: %d distance buckets up to distance %g (2..65536 buckets, the largest distance above half their number and <= 4194304)", li,
@@ -875,7 +877,10 @@ static int gqa_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
   bf16* q16 = sp.n_gqa_tiles > 0 ? static_cast<bf16*>(e->q16) : nullptr;
   if (s.qk_norm == XOTB200_LM_QKNORM_ROW) {
     const int nt = std::min(1024, std::max(128, cdiv(H * dk, 4 * 32) * 32));
-    gqa_prepare_row_kernel<T><<<M, nt, 0, e->stream>>>(e->proj, L.n_in, L.c_q, L.c_kk, L.c_vv, s.proj_bias ? at<T>(e, L.b_in) : nullptr, at<T>(e, L.q_norm),
+    auto pk = gqa_prepare_row_kernel<T>;
+    const size_t psm = (size_t)(H + (own ? G : 0)) * dk * 4;
+    TRY(opt_in_smem(pk, psm));
+    pk<<<M, nt, psm, e->stream>>>(e->proj, L.n_in, L.c_q, L.c_kk, L.c_vv, s.proj_bias ? at<T>(e, L.b_in) : nullptr, at<T>(e, L.q_norm),
                                                         own ? at<T>(e, L.k_norm) : nullptr, e->cfg.norm_eps, H, G, dk, dv, own ? 1 : 0, s.q_temp_coef,
                                                         s.q_temp_every, sp.row_slot, sp.row_pos, pg, pool, e->qfull, q16);
   } else {

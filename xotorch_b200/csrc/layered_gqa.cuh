@@ -119,32 +119,51 @@ __global__ void gqa_prepare_kernel(const float* __restrict__ proj, int ld, int c
 
 // ---------------------------------------------------------------------------------------------------------------------------
 // The same step for layers whose query / key norm runs over the WHOLE projection: q (all H * dk entries of the row, bias added)
-// is divided by its root mean square and multiplied by a weight of that size, and so is k (G * dk entries).  One block per row;
-// two block-wide sums, then every thread writes its share of q (fp32, + bf16 copy), k and v (paged pool).
+// is divided by its root mean square and multiplied by a weight of that size, and so is k (G * dk entries).  One block per row.
+// First pass: every load the row needs (projection, biases, norm weights) is issued at once — the sums of squares are taken, the
+// entries wait in shared memory already multiplied by their norm weight, the values go straight to the pool; one block-wide
+// reduction of both sums; second pass: scale and write q (fp32, + bf16 copy) and k (paged pool).  Dynamic shared memory:
+// (H + G) * dk floats.
 // ---------------------------------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void gqa_prepare_row_kernel(const float* __restrict__ proj, int ld, int col_q, int col_k, int col_v, const T* __restrict__ bias,
                                        const T* __restrict__ q_norm, const T* __restrict__ k_norm, float eps, int H, int G, int dk, int dv, int own_kv,
                                        float q_temp_coef, int q_temp_every, const int* __restrict__ row_slot, const int* __restrict__ row_pos, Paging pg,
                                        T* __restrict__ pool, float* __restrict__ qf, bf16* __restrict__ q16) {
-  __shared__ float red[32];
-  const int m = blockIdx.x, nq = H * dk, nk = G * dk, nv = G * dv;
+  extern __shared__ float qk_row[];                            // [nq] q * q_norm, then [nk] k * k_norm; read back by the writing thread only
+  __shared__ float red[2][32];
+  const int m = blockIdx.x, nq = H * dk, nk = own_kv ? G * dk : 0, nv = own_kv ? G * dv : 0;
   const float* pr = proj + (size_t)m * ld;
+  T* dst = own_kv ? pool + pg.row(row_slot[m], row_pos[m]) * (size_t)(nk + nv) : nullptr;
   float sq = 0.f, sk = 0.f;
-  for (int c = threadIdx.x; c < nq; c += blockDim.x) { const float v = pr[col_q + c] + (bias ? ldf(bias + col_q + c) : 0.f); sq = fmaf(v, v, sq); }
-  if (own_kv)
-    for (int c = threadIdx.x; c < nk; c += blockDim.x) { const float v = pr[col_k + c] + (bias ? ldf(bias + col_k + c) : 0.f); sk = fmaf(v, v, sk); }
-  const float rq = 1.0f / sqrtf(block_sum(sq, red) / (float)nq + eps) * gqa_query_temperature(q_temp_coef, q_temp_every, row_pos[m]);
   for (int c = threadIdx.x; c < nq; c += blockDim.x) {
-    const float v = (pr[col_q + c] + (bias ? ldf(bias + col_q + c) : 0.f)) * rq * ldf(q_norm + c);
+    const float v = pr[col_q + c] + (bias ? ldf(bias + col_q + c) : 0.f);
+    sq = fmaf(v, v, sq);
+    qk_row[c] = v * ldf(q_norm + c);
+  }
+  for (int c = threadIdx.x; c < nk; c += blockDim.x) {
+    const float v = pr[col_k + c] + (bias ? ldf(bias + col_k + c) : 0.f);
+    sk = fmaf(v, v, sk);
+    qk_row[nq + c] = v * ldf(k_norm + c);
+  }
+  for (int c = threadIdx.x; c < nv; c += blockDim.x) stf(dst + nk + c, pr[col_v + c] + (bias ? ldf(bias + col_v + c) : 0.f));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  sq = warp_sum(sq);
+  sk = warp_sum(sk);
+  if (lane == 0) { red[0][warp] = sq; red[1][warp] = sk; }
+  __syncthreads();
+  sq = warp_sum(lane < nw ? red[0][lane] : 0.f);
+  sk = warp_sum(lane < nw ? red[1][lane] : 0.f);
+  const float rq = 1.0f / sqrtf(sq / (float)nq + eps) * gqa_query_temperature(q_temp_coef, q_temp_every, row_pos[m]);
+  for (int c = threadIdx.x; c < nq; c += blockDim.x) {
+    const float v = qk_row[c] * rq;
     qf[(size_t)m * nq + c] = v;
     if (q16) q16[(size_t)m * nq + c] = __float2bfloat16_rn(v);
   }
-  if (!own_kv) return;                                         // block-uniform
-  const float rk = 1.0f / sqrtf(block_sum(sk, red) / (float)nk + eps);
-  T* dst = pool + pg.row(row_slot[m], row_pos[m]) * (size_t)(nk + nv);
-  for (int c = threadIdx.x; c < nk; c += blockDim.x) stf(dst + c, (pr[col_k + c] + (bias ? ldf(bias + col_k + c) : 0.f)) * rk * ldf(k_norm + c));
-  for (int c = threadIdx.x; c < nv; c += blockDim.x) stf(dst + nk + c, pr[col_v + c] + (bias ? ldf(bias + col_v + c) : 0.f));
+  if (nk) {
+    const float rk = 1.0f / sqrtf(sk / (float)nk + eps);
+    for (int c = threadIdx.x; c < nk; c += blockDim.x) stf(dst + c, qk_row[nq + c] * rk);
+  }
 }
 
 // table[a][d] = rel[bucket_of[d], a] for d < n: the learned bias of head a at distance d (rel is [buckets, H] as stored)
