@@ -148,7 +148,7 @@ def layered_numbers(s: dict, prompts, decode_ctx: int, decode_batches, steps: in
   rng = np.random.default_rng(0)
   out = {"weight_bytes": wbytes, "prefill": {}, "decode": {}}
   max_b = max(decode_batches)
-  eng.begin_pool(max(max(prompts), (decode_ctx + steps + warmup + 8) * max_b) + 64, max_b)
+  eng.begin_pool(max(max(prompts), (decode_ctx + steps * 8 + warmup + 8) * max_b) + 64, max_b)   # the decode loop runs warmup + 8 * steps steps
   launches0 = eng.kernel_launches()
   for n in prompts:
     toks = rng.integers(0, s["vocab"], size=n).astype(np.int32)
