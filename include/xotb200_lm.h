@@ -118,10 +118,12 @@ typedef struct xotb200_lm_layer {
   /* -- further options of MIX_ATTENTION -------------------------------------------------------------------------------- */
   int32_t out_bias;     /* 1 = the output projection has a bias (o.b)                                            */
   int32_t sink;         /* 1 = one learned logit per query head (sink) joins the softmax denominator            */
-  int32_t rel_buckets;  /* B > 0: learned bias rel[B, heads] per distance bucket: bucket(n) = n for n < B/2, else
-                           min(B - 1, B/2 + floor(ln(n / (B/2)) / ln(rel_max / (B/2)) * (B - B/2)))              */
-  float rel_max;        /* distance at which the last bucket is reached                                          */
-  float q_temp_coef;    /* != 0: the query at position p is multiplied by 1 + q_temp_coef * ln(floor((p + 1) / q_temp_every) + 1) */
+  int32_t rel_buckets;  /* B > 0: learned bias rel[B, heads] per distance bucket.  With h = B / 2 (integer): distances n < h have a
+                           bucket each (n); the other B - h buckets divide [h, rel_max] in equal steps of ln(n):
+                           bucket = min(B - 1, h + floor((B - h) * ln(n / h) / ln(rel_max / h)))                 */
+  float rel_max;        /* distance at which the last bucket is reached at the latest                            */
+  float q_temp_coef;    /* != 0: the query at position p is multiplied by 1 + q_temp_coef * ln(1 + (p + 1) / q_temp_every), the
+                           quotient taken as an integer                                                          */
   int32_t q_temp_every;
   /* -- further options of FF_MOE ---------------------------------------------------------------------------------------- */
   int32_t expert_act;   /* XOTB200_LM_EXPERT_*                                                                   */

@@ -52,7 +52,7 @@ def distance_bucket(n: int, B: int, far: float) -> int:
 
 
 def query_temperature(T: int, coef: float, every: int, dtype) -> Tensor:
-  """[T]: 1 + coef * ln(floor((p + 1) / every) + 1)"""
+  """[T]: the multiplier of the query at position p, 1 + coef * ln(1 + (p + 1) // every)"""
   return torch.tensor([1.0 + coef * math.log((p + 1) // every + 1) for p in range(T)], dtype=dtype)
 
 

@@ -93,14 +93,14 @@ def tunavik_config(s: dict, b: dict):
   moe = {"kind": "moe", "router": {"experts": EXPERTS, "top": TOP}, "expert": {"ff": ft}, "shared": {"ff": ft}}
   def att(src):
     m = {"heads": b["heads"], "kv_heads": b["kv_heads"], "dim": b["dim"], "vdim": b["vdim"], "scale": float(b["dim"] ** -0.5), "bias_max": REL_FAR,
-         "q_temp": {"coef": 0.5, "every": TEMP_EVERY}}
+         "q_temp": {"coef": 0.3, "every": TEMP_EVERY}}
     if src is not None:
       m["kv_from"] = src
     return {"type": "attention", "mixer": m, "mlp": moe}
   layers = []
   for r in range(s["repeats"]):
     layers += [att(None), att(None), att(3 * r + 1)]
-  cfg = {"architecture": "Tunavik", "width": s["width"], "vocab": s["vocab"], "norm": {"eps": 1e-5}, "logit_scale": 0.5, "logit_softcap": 30.0, "layers": layers}
+  cfg = {"architecture": "Tunavik", "width": s["width"], "vocab": s["vocab"], "norm": {"eps": 1e-6}, "logit_scale": 0.7, "logit_softcap": 50.0, "layers": layers}
   shapes = {f"l{i}.mix.rel": (REL_BUCKETS, b["heads"]) for i in range(len(layers))}
   idle = len(layers) * (EXPERTS - TOP) * 2 * ft * s["width"] * 2
   return cfg, shapes, idle, ft

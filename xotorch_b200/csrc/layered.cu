@@ -1062,7 +1062,7 @@ static int feed_forward(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
     {
       auto kern = moe_rows_up_kernel<T>;
       TRY(opt_in_smem(kern, (size_t)D * 4));
-      // a warp takes two weight rows per round with gated experts (a gate row and its up row), four with ungated ones
+      // a warp takes two weight rows per pass with gated experts (a gate row and its up row), four with ungated ones
       kern<<<dim3(M, top, std::max(1, std::min(cdiv(F, gated ? 8 : 32), M <= 16 ? 1024 : 16))), 256, (size_t)D * 4, e->stream>>>(h, D, at<T>(e, L.w_gu), F, il8, gated ? 1 : 0, e->moe_ids, top, static_cast<T*>(e->mact));
       CK(cudaGetLastError());
       e->launches++;

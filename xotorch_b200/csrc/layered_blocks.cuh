@@ -285,7 +285,7 @@ __device__ __forceinline__ void row_dot4x2(const T* const (&wa)[4], const T* con
   constexpr int VEC = 16 / sizeof(T);
   float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
   if (vec) {
-    for (int k = lane * VEC; k < n; k += 64 * VEC) {           // two pieces of every row per round: sixteen loads in flight per lane
+    for (int k = lane * VEC; k < n; k += 64 * VEC) {           // two pieces of every row per pass: sixteen loads in flight per lane
       const int k2 = k + 32 * VEC;
       const bool more = k2 < n;
       const int kk = more ? k2 : k;                            // past the end the weights read as zero; the index stays inside x
@@ -428,7 +428,7 @@ __global__ void moe_rows_up_kernel(const T* __restrict__ h, int D, const T* __re
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const T* we = w_gu + (size_t)e * (gated ? 2 : 1) * F * D;
   const bool vec = D % (16 / sizeof(T)) == 0 && (reinterpret_cast<uintptr_t>(w_gu) & 15) == 0;
-  if (!gated) {                                                // four up rows per round: four loads in flight per lane
+  if (!gated) {                                                // four up rows per pass: four loads in flight per lane
     const int step = gridDim.z * nw;
     for (int f = blockIdx.z * nw + warp; f < F; f += 4 * step) {
       const T* w4[4];
@@ -460,7 +460,7 @@ __global__ void moe_rows_down_kernel(const T* __restrict__ act, int F, const T* 
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const bool vec = F % (16 / sizeof(T)) == 0 && (reinterpret_cast<uintptr_t>(w_down) & 15) == 0;
-  // two output entries per warp and round (d and d + dstep), the experts of a row four by four, then two by two, in their order:
+  // two output entries per warp and pass (d and d + dstep), the experts of a row four by four, then two by two, in their order:
   // eight weight rows in flight per lane
   const int dstep = gridDim.y * nw;
   for (int d = blockIdx.y * nw + warp; d < D; d += 2 * dstep) {

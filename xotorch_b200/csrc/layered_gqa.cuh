@@ -14,7 +14,7 @@
 //   weights     = softmax over the visible keys (fp32); with a sink the denominator also holds exp(sink[a]), a term that has no
 //                 key, no value, no scale and no bias and counts once; output = sum_j p_j v_j, times sigmoid(gate) per head or
 //                 per entry.
-// Queries may carry a temperature: the query at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1).
+// Queries may carry a temperature: the query at position p is multiplied by 1 + coef * ln(1 + (p + 1) / every), integer quotient.
 //
 // Kernels: gqa_prepare_kernel (bias, per-head RMS norm, temperature, cache append), gqa_prepare_row_kernel (the same with ONE norm
 // over the whole query / key projection), gqa_attention_kernel + gqa_combine_kernel (one warp per (row, query head); decode,
