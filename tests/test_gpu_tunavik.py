@@ -448,6 +448,42 @@ def test_trace_replay_of_a_model_directory(tmp_path):
   rp.close()
 
 
+def test_inference_engine_serves_a_model_directory(tmp_path):
+  """`B200ShardInferenceEngine` (the engine interface the node drives) on a model split over two shards, two request ids
+  interleaved: ensure_shard -> registry -> LayeredShard, the position protocol of infer_tensor, sample(temp 0)"""
+  import asyncio
+  from xotorch_b200.inference.b200_engine import B200ShardInferenceEngine, LocalDirDownloader
+  from xotorch_b200.inference.shard import Shard
+  cfg = config(MIXED)
+  W = to.random_weights(cfg, 27, MIXED_BUCKETS)
+  write_model_dir(tmp_path, cfg, W)
+  n = len(cfg["layers"])
+  first, last = Shard("m", 0, 3, n), Shard("m", 4, n - 1, n)          # the borrowers (layers 2, 3) stay with their owner
+  prompts = {"a": rand_tokens(cfg["vocab"], 9, 1), "b": rand_tokens(cfg["vocab"], 21, 2)}
+
+  async def run():
+    e1 = B200ShardInferenceEngine(LocalDirDownloader({"m": tmp_path}), device=0, max_concurrent_requests=2, max_total_len=64)
+    e2 = B200ShardInferenceEngine(LocalDirDownloader({"m": tmp_path}), device=0, max_concurrent_requests=2, max_total_len=64)
+    out, state, data = {r: [] for r in prompts}, {r: None for r in prompts}, {r: p.reshape(1, -1).astype(np.int64) for r, p in prompts.items()}
+    for _ in range(4):
+      for r in prompts:                               # the two requests take turns, token by token
+        hid, st = await e1.infer_tensor(r, first, data[r], state[r])
+        assert hid.ndim == 3 and hid.shape[2] == cfg["width"]
+        logits, st2 = await e2.infer_tensor(r, last, hid, state[r])
+        tok = await e2.sample(logits, temp=0.0)
+        out[r].append(int(tok[0, 0]))
+        state[r] = st2
+        data[r] = tok.reshape(1, 1).astype(np.int64)
+    return out
+
+  out = asyncio.run(run())
+  for r, p in prompts.items():
+    ids, gaps = oracle_greedy(cfg, W, p, 4)
+    if out[r] != ids:
+      d = next(i for i in range(4) if out[r][i] != ids[i])
+      assert gaps[d] < 0.15, f"{r}: ids leave the oracle's at step {d} with a clear gap"
+
+
 # ---- decode steps replayed from CUDA graphs ----------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_graph_replay_of_decode_steps_changes_nothing(dtype):
