@@ -251,7 +251,7 @@ def test_far_keys_and_page_borders(decode, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("buckets,far", [(8, 20), (16, 100), (6, 37), (2, 3)])
+@pytest.mark.parametrize("buckets,far", [(8, 20), (16, 100), (6, 37), (2, 3), (16, 128)])   # the last: edges that fall exactly on distances 16, 32, 64
 def test_bucket_edges(buckets, far, dtype):
   """Every second bucket of the logarithmic half gets a large bias, the others none: a distance counted into the neighbouring bucket
   (one key too early or too late at an edge, in a prompt, in a portion that starts inside the sequence, or in decoding) changes

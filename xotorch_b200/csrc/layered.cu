@@ -1018,9 +1018,14 @@ static int feed_forward(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
   if (s.ff_kind == XOTB200_LM_FF_MOE) {
     const int E = s.experts, F = s.expert_ff, top = s.top;
     const bool gated = s.expert_act == XOTB200_LM_EXPERT_SILU_GATED;
-    const int shared = s.shared_ff > 0 ? 1 : 0;
+    const int Fs = s.shared_ff;
+    const bool grouped_ok = std::is_same<T, bf16>::value && M >= MOE_GROUPED_MIN_ROWS && e->gemm_mode != 1 && F % 8 == 0 && D % 8 == 0;
+    // Few rows (and the 32-bit mode): the shared expert rides along in the experts' row kernels — no launches and no pass over y of
+    // its own — when the activations of a row fit in shared memory.  Otherwise it runs first as two ordinary products and the
+    // chosen experts' weighted outputs are added to its output.
+    const bool ride = Fs > 0 && !gated && !grouped_ok && ((size_t)top * F + Fs + 4) * 4 <= 200 * 1024;
+    const int shared = Fs > 0 && !ride ? 1 : 0;
     if (shared) {
-      // the shared expert first: y = W_down relu(W_up h)^2; the chosen experts' weighted outputs are then added to it
       TRY((product<T, T, T, 1>(e, h, D, 0, at<T>(e, L.up), D, 1, 0, static_cast<T*>(e->act), s.shared_ff, 0, M, s.shared_ff, D, 1)));
       TRY((product<T, T, float, 0>(e, static_cast<T*>(e->act), s.shared_ff, 0, at<T>(e, L.down), s.shared_ff, 1, 0, e->y, D, 0, M, D, s.shared_ff, 1)));
     }
@@ -1035,7 +1040,7 @@ static int feed_forward(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
     e->launches++;
     const int il8 = gated && F % 8 == 0 ? 1 : 0;
     if constexpr (std::is_same<T, bf16>::value) {
-      if (M >= MOE_GROUPED_MIN_ROWS && e->gemm_mode != 1 && F % 8 == 0 && D % 8 == 0) {
+      if (grouped_ok) {
         const int pairs = M * top, tiles = cdiv(pairs, LTC_M) + E, m_pad = tiles * LTC_M;
         REQUIRE(tiles <= e->moe_tiles_cap, "internal: the expert tile list was not sized for this step");
         int *counts = e->moe_plan, *starts = counts + e->max_experts, *cursor = starts + e->max_experts + 1, *place = cursor + e->max_experts,
@@ -1063,15 +1068,17 @@ static int feed_forward(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
       auto kern = moe_rows_up_kernel<T>;
       TRY(opt_in_smem(kern, (size_t)D * 4));
       // a warp takes two weight rows per pass with gated experts (a gate row and its up row), four with ungated ones
-      kern<<<dim3(M, top, std::max(1, std::min(cdiv(F, gated ? 8 : 32), M <= 16 ? 1024 : 16))), 256, (size_t)D * 4, e->stream>>>(h, D, at<T>(e, L.w_gu), F, il8, gated ? 1 : 0, e->moe_ids, top, static_cast<T*>(e->mact));
+      kern<<<dim3(M, top + (ride ? 1 : 0), std::max(1, std::min(cdiv(std::max(F, ride ? Fs : 0), gated ? 8 : 32), M <= 16 ? 1024 : 16))), 256, (size_t)D * 4, e->stream>>>(
+          h, D, at<T>(e, L.w_gu), F, il8, gated ? 1 : 0, e->moe_ids, top, static_cast<T*>(e->mact), ride ? at<T>(e, L.up) : nullptr, Fs, static_cast<T*>(e->act));
       CK(cudaGetLastError());
       e->launches++;
     }
     {
       auto kern = moe_rows_down_kernel<T>;
-      TRY(opt_in_smem(kern, (size_t)top * F * 4));
-      kern<<<dim3(M, std::max(1, std::min(cdiv(D, 16), M <= 16 ? 1024 : 16))), 256, (size_t)top * F * 4, e->stream>>>(static_cast<T*>(e->mact), F, at<T>(e, L.w_edown), D, e->moe_ids, e->moe_wts,
-                                                                                                   top, shared, e->y);
+      const size_t dsm = ((size_t)top * F + (ride ? Fs + 4 : 0)) * 4;
+      TRY(opt_in_smem(kern, dsm));
+      kern<<<dim3(M, std::max(1, std::min(cdiv(D, 16), M <= 16 ? 1024 : 16))), 256, dsm, e->stream>>>(static_cast<T*>(e->mact), F, at<T>(e, L.w_edown), D, e->moe_ids, e->moe_wts, top,
+                                                                                                   shared, e->y, static_cast<T*>(e->act), ride ? at<T>(e, L.down) : nullptr, Fs);
       CK(cudaGetLastError());
       e->launches++;
     }

@@ -415,20 +415,24 @@ __device__ __host__ __forceinline__ size_t moe_up_row(int f, int F, int il8) { r
 //   moe_rows_up_kernel   act[m, k, f] = silu(W_gate[e] h_m)[f] * (W_up[e] h_m)[f],  e = ids[m, k]        one warp per f
 //                        ungated experts (w_gu is then [E][F, D], up rows only): act[m, k, f] = relu(W_up[e] h_m)[f]^2
 //   moe_rows_down_kernel y[m, d] (+)= sum_k wts[m, k] * (W_down[e_k] act[m, k, :])[d]                    one warp per d
-// w_down: [E][D, F].  With `accumulate` the sum is added to what y holds (a shared expert's output).
+// w_down: [E][D, F].  With `accumulate` the sum is added to what y holds (a shared expert's output made by ordinary products).
+// A shared expert of ungated form can also ride along: w_shared [Fs, D] is one more "expert" of moe_rows_up_kernel (grid y = top,
+// its activations go to act_shared [M, Fs]), and moe_rows_down_kernel adds W_sdown act_shared with weight one (w_sdown [D, Fs]).
 // ---------------------------------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void moe_rows_up_kernel(const T* __restrict__ h, int D, const T* __restrict__ w_gu, int F, int il8, int gated, const int* __restrict__ ids,
-                                   int top, T* __restrict__ act) {
+                                   int top, T* __restrict__ act, const T* __restrict__ w_shared, int Fs, T* __restrict__ act_shared) {
   extern __shared__ __align__(16) float hs[];                  // the row, fp32
   const int m = blockIdx.x, k = blockIdx.y;
-  const int e = ids[(size_t)m * top + k];
   for (int d = threadIdx.x; d < D; d += blockDim.x) hs[d] = ldf(h + (size_t)m * D + d);
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  const T* we = w_gu + (size_t)e * (gated ? 2 : 1) * F * D;
-  const bool vec = D % (16 / sizeof(T)) == 0 && (reinterpret_cast<uintptr_t>(w_gu) & 15) == 0;
+  const bool vec = D % (16 / sizeof(T)) == 0 && (reinterpret_cast<uintptr_t>(w_gu) & 15) == 0 && (reinterpret_cast<uintptr_t>(w_shared) & 15) == 0;
   if (!gated) {                                                // four up rows per pass: four loads in flight per lane
+    const bool sh = k == top;                                  // the shared expert rides along as grid row `top`
+    const T* we = sh ? w_shared : w_gu + (size_t)ids[(size_t)m * top + k] * F * D;
+    T* out = sh ? act_shared + (size_t)m * Fs : act + ((size_t)m * top + k) * F;
+    if (sh) F = Fs;
     const int step = gridDim.z * nw;
     for (int f = blockIdx.z * nw + warp; f < F; f += 4 * step) {
       const T* w4[4];
@@ -440,11 +444,12 @@ __global__ void moe_rows_up_kernel(const T* __restrict__ h, int D, const T* __re
       if (lane == 0) {
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-          if (f + i * step < F) { const float r = fmaxf(u[i], 0.f); stf(act + ((size_t)m * top + k) * F + f + i * step, r * r); }
+          if (f + i * step < F) { const float r = fmaxf(u[i], 0.f); stf(out + f + i * step, r * r); }
       }
     }
     return;
   }
+  const T* we = w_gu + (size_t)ids[(size_t)m * top + k] * 2 * F * D;
   for (int f = blockIdx.z * nw + warp; f < F; f += gridDim.z * nw) {
     float g, u;
     row_dot2(we + moe_gate_row(f, F, il8) * D, we + moe_up_row(f, F, il8) * D, hs, hs, D, lane, vec, g, u);
@@ -453,13 +458,18 @@ __global__ void moe_rows_up_kernel(const T* __restrict__ h, int D, const T* __re
 }
 template <typename T>
 __global__ void moe_rows_down_kernel(const T* __restrict__ act, int F, const T* __restrict__ w_down, int D, const int* __restrict__ ids,
-                                     const float* __restrict__ wts, int top, int accumulate, float* __restrict__ y) {
-  extern __shared__ __align__(16) float as[];                  // [top][F] fp32
+                                     const float* __restrict__ wts, int top, int accumulate, float* __restrict__ y, const T* __restrict__ act_shared,
+                                     const T* __restrict__ w_sdown, int Fs) {
+  extern __shared__ __align__(16) float as[];                  // [top][F] fp32, then [Fs] of the shared expert (from a 16-byte boundary)
   const int m = blockIdx.x;
+  float* as_s = as + (((size_t)top * F + 3) & ~(size_t)3);
   for (int i = threadIdx.x; i < top * F; i += blockDim.x) as[i] = ldf(act + (size_t)m * top * F + i);
+  if (w_sdown)
+    for (int i = threadIdx.x; i < Fs; i += blockDim.x) as_s[i] = ldf(act_shared + (size_t)m * Fs + i);
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const bool vec = F % (16 / sizeof(T)) == 0 && (reinterpret_cast<uintptr_t>(w_down) & 15) == 0;
+  const bool vec_s = Fs % (16 / sizeof(T)) == 0 && (reinterpret_cast<uintptr_t>(w_sdown) & 15) == 0;
   // two output entries per warp and pass (d and d + dstep), the experts of a row four by four, then two by two, in their order:
   // eight weight rows in flight per lane
   const int dstep = gridDim.y * nw;
@@ -501,6 +511,12 @@ __global__ void moe_rows_down_kernel(const T* __restrict__ act, int F, const T* 
       row_dot2(w_down + (ex + d) * F, w_down + (ex + d2) * F, as + k * F, as + k * F, F, lane, vec, r0, r1);
       out = fmaf(wts[(size_t)m * top + k], r0, out);
       out2 = fmaf(wts[(size_t)m * top + k], r1, out2);
+    }
+    if (w_sdown) {                                             // the shared expert: weight one
+      float r0, r1;
+      row_dot2(w_sdown + (size_t)d * Fs, w_sdown + (size_t)d2 * Fs, as_s, as_s, Fs, lane, vec_s, r0, r1);
+      out += r0;
+      out2 += r1;
     }
     if (lane == 0) {
       y[(size_t)m * D + d] = accumulate ? y[(size_t)m * D + d] + out : out;
