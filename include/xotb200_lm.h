@@ -14,9 +14,16 @@
  *                               penalty, learned bias per distance bucket, query temperature, softmax sink, sliding window,
  *                               block-local mask, output gate per head or per entry, keys/values borrowed from an earlier layer;
  *   XOTB200_LM_MIX_GATED_DELTA  delta rule with one decay per head behind short causal convolutions;
- *                               state = fp32 matrix per head + the convolutions' last inputs.
+ *                               state = fp32 matrix per head + the convolutions' last inputs;
+ *   XOTB200_LM_MIX_MATRIX_LSTM  matrix memory with exponential input gate, sigmoid forget gate and a running maximum that keeps both
+ *                               in range; state = fp32 matrix + normaliser vector + maximum per head;
+ *   XOTB200_LM_MIX_MAMBA2       state-space layer with one decay per head, input-dependent step size, short convolution on its
+ *                               inputs, gate before a grouped RMS norm; state = fp32 matrix per head + the convolution's last inputs.
+ * Any of the attention, gated-delta, matrix-LSTM and state-space mixers may run as the SECOND branch of a layer (par_on): both read
+ * the same input (one product for all their projections) and the layer's mixer output is mix_scale * first + par_scale * second.
  * A layer wraps its sublayers in grouped RMS norms before and after them, or reads the stream itself and closes with a layer norm
- * or an RMS norm (xotb200_lm_cfg.block); its feed-forward is dense (relu^2 or xIELU) or a mixture of experts (gated silu or relu^2
+ * or an RMS norm, or — pre-norm with one-number weights — reads `streams` copies of the residual stream through hyper-connections
+ * and passes every sublayer input through a short causal convolution that is added to it (xotb200_lm_cfg.block); its feed-forward is dense (relu^2 or xIELU) or a mixture of experts (gated silu or relu^2
  * experts, two routing rules, an optional shared expert: xotb200_lm_layer.ff_kind and the fields after it).
  * Every size and constant of a layer is a field of xotb200_lm_layer, so a model family is a table of layers, not code.
  *
@@ -52,10 +59,13 @@ extern "C" {
 #define XOTB200_LM_MIX_DELTA_RULE 1
 #define XOTB200_LM_MIX_ATTENTION 2   /* grouped-query attention over a paged key/value cache (see xotb200_lm_layer)            */
 #define XOTB200_LM_MIX_GATED_DELTA 3 /* delta rule with one decay per head behind short causal convolutions                    */
+#define XOTB200_LM_MIX_MATRIX_LSTM 4 /* matrix memory: S <- e^(f + m' - m) S + e^(i - m) k v^T with running maximum m              */
+#define XOTB200_LM_MIX_MAMBA2 5      /* state-space layer: S <- e^(-e^A dt) S + dt B x^T, y = S^T C + D x                          */
 
 #define XOTB200_LM_FF_RELU2 0  /* W_down relu(W_up h)^2                                                                         */
 #define XOTB200_LM_FF_XIELU 1  /* W_down act(W_up h), act(z) = softplus(p) z^2 + z/2 (z > 0), (1/2 + softplus(q))(e^z - 1 - z) + z/2 (z <= 0);
                                   p, q = the two entries of l<i>.mlp.act                                                         */
+#define XOTB200_LM_FF_GELU 3   /* W_down gelu(W_up h), the exact gelu z (1 + erf(z / sqrt 2)) / 2                               */
 #define XOTB200_LM_FF_MOE 2    /* mixture of experts; expert form, routing rule and shared expert: expert_act, router_kind, shared_ff */
 
 #define XOTB200_LM_EXPERT_SILU_GATED 0 /* expert = W_down (silu(W_gate h) * W_up h)                                              */
@@ -68,8 +78,13 @@ extern "C" {
 #define XOTB200_LM_BLOCK_POST_LN 1    /* x += LN(mixer(x)): the sublayer reads the stream itself, layer norm (weight + bias) on its output */
 #define XOTB200_LM_BLOCK_POST_RMS 2   /* x += rms(mixer(x)) * (1 + w): the same with an RMS norm whose weight is stored around zero     */
 
+#define XOTB200_LM_BLOCK_PRE_SCALAR 3  /* x += mult * sublayer(c(rms(x) * g)): pre-norm whose weight is ONE number, c(h) = h + causal
+                                         convolution of h over time (canon_taps; 0 = none); with streams > 0 the stream is kept in
+                                         `streams` copies mixed by hyper-connections (below); embedding and final norm of the same kind */
+
 #define XOTB200_LM_QKNORM_NONE 0
 #define XOTB200_LM_QKNORM_HEAD 1      /* RMS norm of every query / key head, one weight of size dim shared by the heads                 */
+#define XOTB200_LM_QKNORM_HEAD_PLAIN 3 /* every query / key head divided by its root mean square, no weight                            */
 #define XOTB200_LM_QKNORM_ROW 2       /* ONE RMS norm over the whole query (key) projection, weights of size heads * dim (kv_heads * dim) */
 
 #define XOTB200_LM_ROT_INTERLEAVED 0 /* pairs (2i, 2i+1)        */
@@ -130,6 +145,31 @@ typedef struct xotb200_lm_layer {
   int32_t router_kind;  /* XOTB200_LM_ROUTER_*                                                                   */
   int32_t router_bias;  /* 1 = the router logits have a bias (router.b)                                          */
   int32_t shared_ff;    /* > 0: a shared expert of this inner size (same form as the experts) runs for every token and is added */
+  /* -- further options of MIX_ATTENTION: rotation of queries and keys, kept first tokens, pooled far blocks --------------------
+   * rot_dims > 0: the first rot_dims entries of every query and key head are rotated by the token's position (rot_layout, rot_base;
+   * the cache holds rotated keys).  rot_scale_factor > 0: with wavelength l = 2 pi / f, f stays where l < original / high, becomes
+   * f / factor where l > original / low, and in between (1 - s) f / factor + s f with s = (original / l - low) / (high - low).
+   * keep_first > 0 (with a window): the first keep_first tokens of the request stay visible whatever the distance.
+   * pool > 0 (with a window): every block of `pool` consecutive tokens (blocks counted from position 0) that lies wholly before a
+   * row's window, b * pool + pool - 1 <= i - window, is seen as ONE key and value: the means of the block's cached keys and values. */
+  float rot_scale_factor, rot_scale_low, rot_scale_high, rot_scale_original;
+  int32_t keep_first;
+  int32_t pool;
+  /* -- MIX_MATRIX_LSTM: heads x (dim, vdim); q = W_q h / sqrt(dim), k, v; log gates i = cap tanh((W_i h + b) / cap),
+   * f = logsigmoid(cap tanh((W_f h + b) / cap)); m <- max(f + m, i) (m starts at 0); S <- e^(f + m_old - m) S + e^(i - m) k v^T, n likewise
+   * with k alone; o = S^T q / (max(|n.q|, e^-m) + 1e-6); o / rms(o) * norm (heads * vdim) * sigmoid(W_g h).
+   * MIX_MAMBA2: heads x vdim channels, state size `dim`, `kv_heads` groups of B / C; W_in h = [z | x | B | C | dt]; x, B, C through a
+   * causal filter of conv_taps taps with bias and silu; dt <- softplus(dt + dt_bias); per head S <- e^(-e^A_log dt) S + dt B x^T,
+   * y = S^T C + D x; (y * silu(z)) RMS-normed in out_norm_groups equal parts, times norm; W_o. */
+  float gate_cap;
+  int32_t out_norm_groups;
+  /* -- a second mixer in the same layer (par_on = 1): tensors l<i>.mix.left.* (this mixer) and l<i>.mix.right.* (the second) ------ */
+  int32_t par_on;
+  int32_t par_mixer;    /* XOTB200_LM_MIX_GATED_DELTA, MIX_MATRIX_LSTM, MIX_MAMBA2 or MIX_ATTENTION                              */
+  int32_t par_heads, par_kv_heads, par_dim, par_vdim, par_conv_taps, par_out_norm_groups;
+  float par_gate_cap;
+  float mix_scale;      /* the layer's mixer output = mix_scale * this mixer (0 = 1) + par_scale * the second                    */
+  float par_scale;
 } xotb200_lm_layer;
 
 typedef struct xotb200_lm_cfg {
@@ -149,6 +189,13 @@ typedef struct xotb200_lm_cfg {
   int32_t embed_norm;    /* 1 = the block's closing norm (weight embed.norm) is applied to the embedding sum before the first layer */
   float logit_scale;     /* logits are multiplied by this (0 = 1)                                                                   */
   float logit_softcap;   /* > 0: logits <- cap * tanh(logits / cap), after the scale                                                */
+  /* -- BLOCK_PRE_SCALAR ------------------------------------------------------------------------------------------------------
+   * streams > 0: hyper-connections.  The stream is kept in `streams` copies X_1 .. X_s (all equal to the embedding output at the
+   * start); sublayer q of a layer reads u = sum_s in[s] X_s and writes X_t <- sum_s mix[s, t] X_s + mult * out[t] * y for all t at
+   * once (tensors l<i>.hc<q>.in / out / mix); the model's output stream is the sum of the copies.  streams = 0: x += mult * y. */
+  int32_t streams;
+  int32_t canon_taps;    /* > 0: taps of the convolution on every sublayer input (l<i>.canon<q> [width, taps], last tap = current token) */
+  float residual_mult;   /* 0 = 1                                                                                                   */
 } xotb200_lm_cfg;
 
 typedef struct xotb200_lm xotb200_lm;
@@ -168,6 +215,9 @@ int xotb200_lm_destroy(xotb200_lm* e);
  * BLOCK_POST_RMS models: l<i>.norm1 / norm2, embed.norm; further MIX_ATTENTION tensors: o.b, sink [heads], rel [buckets, heads]; with
  * QKNORM_ROW q.norm / k.norm have the projection's size; further FF_MOE tensors: router.b, shared.up / shared.down; relu^2 experts
  * have no gate matrix.
+ * BLOCK_PRE_SCALAR models: embed.norm, final.norm, l<i>.norm1 / norm2 (one number each), l<i>.canon1 / canon2, l<i>.hc1 / hc2 .in / .out /
+ * .mix; MIX_ATTENTION with QKNORM_HEAD_PLAIN has no norm weights; MIX_MATRIX_LSTM <t> in {q, k, v, g, i, i.b, f, f.b, norm, o};
+ * MIX_MAMBA2 <t> in {in, conv, conv.b, dt_bias, A_log, D, norm, o}; a layer with two mixers names them l<i>.mix.left.<t> / .right.<t>.
  * xotb200_lm_load_dir reads every *.safetensors of the directory (BF16 tensors) and is STRICT: a tensor of this shard that is
  * missing, has another shape or dtype, or an unknown tensor of an owned layer, is an error. */
 int xotb200_lm_load_dir(xotb200_lm* e, const char* dir);

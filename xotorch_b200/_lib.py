@@ -100,12 +100,12 @@ def load(path: os.PathLike | None = None) -> C.CDLL:
 # ---- libxotb200_lm.so: the layered-model engine (include/xotb200_lm.h) --------------------------------------------------
 LM_LIB_PATH = Path(__file__).resolve().parent / "lib" / "libxotb200_lm.so"
 LM_DTYPE_BF16, LM_DTYPE_F32 = 0, 2
-LM_MIX_LATENT_ATTN, LM_MIX_DELTA_RULE, LM_MIX_ATTENTION, LM_MIX_GATED_DELTA = 0, 1, 2, 3
-LM_FF_RELU2, LM_FF_XIELU, LM_FF_MOE = 0, 1, 2
+LM_MIX_LATENT_ATTN, LM_MIX_DELTA_RULE, LM_MIX_ATTENTION, LM_MIX_GATED_DELTA, LM_MIX_MATRIX_LSTM, LM_MIX_MAMBA2 = 0, 1, 2, 3, 4, 5
+LM_FF_RELU2, LM_FF_XIELU, LM_FF_MOE, LM_FF_GELU = 0, 1, 2, 3
 LM_EXPERT_SILU_GATED, LM_EXPERT_RELU2 = 0, 1
 LM_ROUTER_SOFTMAX_ALL, LM_ROUTER_TOPK_SOFTMAX = 0, 1
-LM_BLOCK_GROUP_RMS, LM_BLOCK_POST_LN, LM_BLOCK_POST_RMS = 0, 1, 2
-LM_QKNORM_NONE, LM_QKNORM_HEAD, LM_QKNORM_ROW = 0, 1, 2
+LM_BLOCK_GROUP_RMS, LM_BLOCK_POST_LN, LM_BLOCK_POST_RMS, LM_BLOCK_PRE_SCALAR = 0, 1, 2, 3
+LM_QKNORM_NONE, LM_QKNORM_HEAD, LM_QKNORM_ROW, LM_QKNORM_HEAD_PLAIN = 0, 1, 2, 3
 LM_ROT_INTERLEAVED, LM_ROT_HALF = 0, 1
 
 
@@ -121,6 +121,11 @@ class LmLayer(C.Structure):
     ("out_bias", C.c_int32), ("sink", C.c_int32), ("rel_buckets", C.c_int32), ("rel_max", C.c_float), ("q_temp_coef", C.c_float),
     ("q_temp_every", C.c_int32), ("expert_act", C.c_int32), ("router_kind", C.c_int32), ("router_bias", C.c_int32),
     ("shared_ff", C.c_int32),
+    ("rot_scale_factor", C.c_float), ("rot_scale_low", C.c_float), ("rot_scale_high", C.c_float), ("rot_scale_original", C.c_float),
+    ("keep_first", C.c_int32), ("pool", C.c_int32), ("gate_cap", C.c_float), ("out_norm_groups", C.c_int32),
+    ("par_on", C.c_int32), ("par_mixer", C.c_int32), ("par_heads", C.c_int32), ("par_kv_heads", C.c_int32), ("par_dim", C.c_int32),
+    ("par_vdim", C.c_int32), ("par_conv_taps", C.c_int32), ("par_out_norm_groups", C.c_int32), ("par_gate_cap", C.c_float),
+    ("mix_scale", C.c_float), ("par_scale", C.c_float),
   ]
 
 
@@ -129,7 +134,7 @@ class LmCfg(C.Structure):
     ("n_layers", C.c_int32), ("start_layer", C.c_int32), ("end_layer", C.c_int32), ("width", C.c_int32), ("vocab", C.c_int32),
     ("norm_groups", C.c_int32), ("dtype", C.c_int32), ("norm_eps", C.c_float), ("block", C.c_int32), ("max_positions", C.c_int32),
     ("pos_sinusoid", C.c_int32), ("sinusoid_base", C.c_float), ("embed_norm", C.c_int32), ("logit_scale", C.c_float),
-    ("logit_softcap", C.c_float),
+    ("logit_softcap", C.c_float), ("streams", C.c_int32), ("canon_taps", C.c_int32), ("residual_mult", C.c_float),
   ]
 
 

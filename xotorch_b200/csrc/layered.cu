@@ -29,6 +29,7 @@
 #include "layered_kernels.cuh"
 #include "layered_blocks.cuh"
 #include "layered_gqa.cuh"
+#include "layered_recurrent.cuh"
 #include "layered_tc.cuh"
 #include "st_header.h"
 
@@ -99,6 +100,14 @@ struct LmLayer {
   size_t conv_off = 0;                                 // float offset of the filter inputs inside a slot's state block
   // feed-forward forms: xIELU parameters; mixture of experts: router [E, D], experts' [E][2 F, D] (gate rows, up rows) and [E][D, F]
   size_t act_p = 0, router = 0, router_b = 0, w_gu = 0, w_edown = 0;   // a shared expert's matrices are `up` / `down`
+  // matrix LSTM: gate biases, float offset of the running maxima in a slot's block; state-space layer: filter bias, skip weights
+  size_t i_b = 0, f_b = 0, conv_b = 0, d_skip = 0, m_off = 0;
+  int c_i = 0, c_f = 0, c_z = 0, c_dt = 0;
+  int ld_in = 0;                                       // leading dimension of the projection output this mixer reads (all mixers of the layer)
+  std::vector<LmLayer> par;                            // the layer's second mixer (0 or 1 entries): reads the same input, output added
+  // pre-norm block with one-number weights: convolutions on the sublayer inputs ([D, taps]), their inputs' place in a slot's state
+  // block, hyper-connection coefficients (in [S], out [S], mix [S, S]) of the two sublayers
+  size_t canon[2] = {0, 0}, canon_off[2] = {0, 0}, hc_in[2] = {0, 0}, hc_out[2] = {0, 0}, hc_mix[2] = {0, 0};
   float* freqs = nullptr;                              // [rot_dims / 2] fp32 on the device
   void* pool = nullptr;                                // paged pool [n_pages * P, row] of T: latent + rotated key part, or keys + values
   size_t state_off = 0;                                // delta rules: float offset of this layer's state inside a slot's block
@@ -148,6 +157,10 @@ struct xotb200_lm {
   float* dist_tab = nullptr;                           // prompt attention: distance penalties per head and distance, remade per layer
   size_t dist_cap = 0;
   int max_conv = 0, max_top = 0, max_eff = 0, max_experts = 0;
+  float *y2 = nullptr, *h0 = nullptr, *gdec = nullptr, *ginw = nullptr, *gfloor = nullptr, *vaug = nullptr;   // second mixer's output, normed input
+                                                       // before its convolution, matrix-LSTM gates per (row, head), values with the normaliser column
+  int max_heads_rec = 0, max_vaug = 0;
+  bool pre_scalar = false;
   size_t final_norm_b = 0, pos_table = 0;
   void *h = nullptr, *cqn = nullptr, *qn = nullptr, *olat = nullptr, *oh = nullptr, *act = nullptr, *th = nullptr, *hw = nullptr;
   void *q16 = nullptr, *cbuf = nullptr, *knx = nullptr, *vxx = nullptr;   // expanded prompt attention (bf16)
@@ -181,6 +194,18 @@ template <typename T> static T* at(xotb200_lm* e, size_t off) { return reinterpr
 // ---------------------------------------------------------------------------------------------------------------------------
 // layout
 // ---------------------------------------------------------------------------------------------------------------------------
+// columns of the projection a mixer reads (every matrix that multiplies the sublayer's input)
+static int mixer_columns(const xotb200_lm_layer& s) {
+  switch (s.mixer) {
+    case XOTB200_LM_MIX_ATTENTION:
+      return s.heads * s.dim + (s.kv_from < 0 ? s.kv_heads * (s.dim + s.vdim) : 0) + (s.out_gate == 2 ? s.heads * s.vdim : s.out_gate == 1 ? s.heads : 0);
+    case XOTB200_LM_MIX_GATED_DELTA: return 2 * s.kv_heads * s.dim + 2 * s.heads * s.vdim + 2 * s.heads;
+    case XOTB200_LM_MIX_MATRIX_LSTM: return 2 * s.heads * s.dim + 2 * s.heads * s.vdim + 2 * s.heads;
+    case XOTB200_LM_MIX_MAMBA2: return 2 * s.heads * s.vdim + 2 * s.kv_heads * s.dim + s.heads;
+    default: return 0;
+  }
+}
+
 static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
   const int D = e->cfg.width, V = e->cfg.vocab;
   size_t cur = 0;
@@ -188,12 +213,30 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
   auto take = [&](size_t n) { size_t o = cur; cur = align_up(cur + n, al); return o; };
   auto dest = [&](const std::string& name, size_t off, int rows, int cols, int row_off) { e->dests[name] = Dest{off, rows, cols, row_off, false}; };
   const bool post_ln = e->cfg.block == XOTB200_LM_BLOCK_POST_LN, post_rms = e->cfg.block == XOTB200_LM_BLOCK_POST_RMS;
+  const bool pre_scalar = e->cfg.block == XOTB200_LM_BLOCK_PRE_SCALAR;
+  const int NW = pre_scalar ? 1 : D;                   // entries of a block norm's weight
+  const int S = e->cfg.streams, CT = e->cfg.canon_taps;
+  e->pre_scalar = pre_scalar;
+  // what a sublayer of the pre-scalar block owns besides its norm: input convolution and hyper-connection coefficients
+  auto sublayer_extras = [&](LmLayer& L, const std::string& p, int q) {
+    const std::string n = std::to_string(q + 1);
+    if (CT > 0) {
+      L.canon[q] = take((size_t)D * CT); dest(p + "canon" + n, L.canon[q], D, CT, 0);
+      L.canon_off[q] = e->state_floats;
+      e->state_floats += (size_t)(CT - 1) * D;
+    }
+    if (S > 0) {
+      L.hc_in[q] = take(S); dest(p + "hc" + n + ".in", L.hc_in[q], 1, S, 0);
+      L.hc_out[q] = take(S); dest(p + "hc" + n + ".out", L.hc_out[q], 1, S, 0);
+      L.hc_mix[q] = take((size_t)S * S); dest(p + "hc" + n + ".mix", L.hc_mix[q], S, S, 0);
+    }
+  };
   // the weight after a sublayer: a second grouped RMS norm ("norm1b"), or the bias of the closing layer norm ("norm1.b"); a closing
   // RMS norm has one weight only
   const std::string nb = post_ln ? ".b" : "b";
   if (e->first) {
     e->embed = take((size_t)V * D); dest("embed", e->embed, V, D, 0);
-    if (e->cfg.embed_norm) { e->embed_norm = take(D); dest("embed.norm", e->embed_norm, 1, D, 0); }
+    if (e->cfg.embed_norm) { e->embed_norm = take(NW); dest("embed.norm", e->embed_norm, 1, NW, 0); }
     if (e->cfg.max_positions > 0) { e->pos_table = take((size_t)e->cfg.max_positions * D); dest("pos", e->pos_table, e->cfg.max_positions, D, 0); }
   }
   for (int li = e->cfg.start_layer; li <= e->cfg.end_layer; ++li) {
@@ -202,8 +245,14 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
     const xotb200_lm_layer& s = L.s;
     const std::string p = "l" + std::to_string(li) + ".";
     REQUIRE(s.heads >= 1 && s.dim >= 1, "layer %d: heads and dim must be positive", li);
-    L.norm1 = take(D); dest(p + "norm1", L.norm1, 1, D, 0);
-    if (!post_rms) { L.norm1b = take(D); dest(p + "norm1" + nb, L.norm1b, 1, D, 0); }
+    L.norm1 = take(NW); dest(p + "norm1", L.norm1, 1, NW, 0);
+    if (!post_rms && !pre_scalar) { L.norm1b = take(D); dest(p + "norm1" + nb, L.norm1b, 1, D, 0); }
+    if (pre_scalar) sublayer_extras(L, p, 0);
+    // one mixer: its projection columns start at column cb of the layer's projection output; `shared`: the projection matrix of
+    // the layer's mixers is one allocation (w_shared) and this mixer's rows follow the first mixer's
+    auto layout_mixer = [&](LmLayer& L, const std::string& mp, int cb, bool shared, size_t w_shared) -> int {
+    const xotb200_lm_layer& s = L.s;
+    REQUIRE(!shared || (s.mixer != XOTB200_LM_MIX_LATENT_ATTN && s.mixer != XOTB200_LM_MIX_DELTA_RULE), "layer %d: this mixer kind cannot share a layer", li);
     if (s.mixer == XOTB200_LM_MIX_LATENT_ATTN) {
       const int H = s.heads, dn = s.dim, dr = s.rot_dim, dv = s.vdim, R = s.kv_rank, HQ = H * (dn + dr);
       REQUIRE(R >= 1 && R <= 512, "layer %d: kv_rank %d outside 1..512", li, R);
@@ -213,22 +262,22 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
       const int nq = s.q_rank > 0 ? s.q_rank : HQ;
       L.c_q = 0; L.c_kv = nq; L.c_g = nq + R + dr;
       L.n_in = nq + R + dr + (s.out_gate ? H : 0);
-      L.w_in = take((size_t)L.n_in * D);
+      L.w_in = shared ? w_shared : take((size_t)L.n_in * D);
       if (s.q_rank > 0) {
-        dest(p + "mix.dq", L.w_in, s.q_rank, D, 0);
-        L.dq_norm = take(s.q_rank); dest(p + "mix.dq.norm", L.dq_norm, 1, s.q_rank, 0);
-        L.uq = take((size_t)HQ * s.q_rank); dest(p + "mix.uq", L.uq, HQ, s.q_rank, 0);
+        dest(mp + "dq", L.w_in, s.q_rank, D, 0);
+        L.dq_norm = take(s.q_rank); dest(mp + "dq.norm", L.dq_norm, 1, s.q_rank, 0);
+        L.uq = take((size_t)HQ * s.q_rank); dest(mp + "uq", L.uq, HQ, s.q_rank, 0);
       } else {
-        dest(p + "mix.q", L.w_in, HQ, D, 0);
+        dest(mp + "q", L.w_in, HQ, D, 0);
       }
-      dest(p + "mix.dkv", L.w_in, R + dr, D, L.c_kv);
-      if (s.out_gate) dest(p + "mix.g", L.w_in, H, D, L.c_g);
-      L.dkv_norm = take(R); dest(p + "mix.dkv.norm", L.dkv_norm, 1, R, 0);
+      dest(mp + "dkv", L.w_in, R + dr, D, L.c_kv);
+      if (s.out_gate) dest(mp + "g", L.w_in, H, D, L.c_g);
+      L.dkv_norm = take(R); dest(mp + "dkv.norm", L.dkv_norm, 1, R, 0);
       // W_uk is kept per head as [R, dn]: the absorption product q~ = W_uk[h]^T q then reads it K-major like every other weight
-      L.uk = take((size_t)H * dn * R); dest(p + "mix.uk", L.uk, H * dn, R, 0); e->dests[p + "mix.uk"].tr_heads = H;
-      L.uk_rows = take((size_t)H * dn * R); e->dests[p + "mix.uk"].has2 = true; e->dests[p + "mix.uk"].elem_off2 = L.uk_rows;
-      L.uv = take((size_t)H * dv * R); dest(p + "mix.uv", L.uv, H * dv, R, 0);
-      L.wo = take((size_t)D * H * dv); dest(p + "mix.o", L.wo, D, H * dv, 0);
+      L.uk = take((size_t)H * dn * R); dest(mp + "uk", L.uk, H * dn, R, 0); e->dests[mp + "uk"].tr_heads = H;
+      L.uk_rows = take((size_t)H * dn * R); e->dests[mp + "uk"].has2 = true; e->dests[mp + "uk"].elem_off2 = L.uk_rows;
+      L.uv = take((size_t)H * dv * R); dest(mp + "uv", L.uv, H * dv, R, 0);
+      L.wo = take((size_t)D * H * dv); dest(mp + "o", L.wo, D, H * dv, 0);
       e->max_q = std::max(e->max_q, HQ);
       e->max_qfull = std::max(e->max_qfull, H * (R + dr));
       e->max_qr = std::max(e->max_qr, s.q_rank);
@@ -246,18 +295,18 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
       REQUIRE(s.low_rank >= 1, "layer %d: the decay branch needs an inner size", li);
       L.c_r = 0; L.c_k = HD; L.c_v = 2 * HD; L.c_g = 3 * HD; L.c_a = 4 * HD; L.c_w1 = 5 * HD;
       L.n_in = 5 * HD + s.low_rank;
-      L.w_in = take((size_t)L.n_in * D);
-      dest(p + "mix.r", L.w_in, HD, D, L.c_r);
-      dest(p + "mix.k", L.w_in, HD, D, L.c_k);
-      dest(p + "mix.v", L.w_in, HD, D, L.c_v);
-      dest(p + "mix.g", L.w_in, HD, D, L.c_g);
-      dest(p + "mix.a", L.w_in, HD, D, L.c_a);
-      dest(p + "mix.w1", L.w_in, s.low_rank, D, L.c_w1);
-      L.w2 = take((size_t)HD * s.low_rank); dest(p + "mix.w2", L.w2, HD, s.low_rank, 0);
-      L.w0 = take(HD); dest(p + "mix.w0", L.w0, 1, HD, 0);
-      L.a_b = take(HD); dest(p + "mix.a.b", L.a_b, 1, HD, 0);
-      L.onorm = take(HD); dest(p + "mix.norm", L.onorm, 1, HD, 0);
-      L.wo = take((size_t)D * HD); dest(p + "mix.o", L.wo, D, HD, 0);
+      L.w_in = shared ? w_shared : take((size_t)L.n_in * D);
+      dest(mp + "r", L.w_in, HD, D, L.c_r);
+      dest(mp + "k", L.w_in, HD, D, L.c_k);
+      dest(mp + "v", L.w_in, HD, D, L.c_v);
+      dest(mp + "g", L.w_in, HD, D, L.c_g);
+      dest(mp + "a", L.w_in, HD, D, L.c_a);
+      dest(mp + "w1", L.w_in, s.low_rank, D, L.c_w1);
+      L.w2 = take((size_t)HD * s.low_rank); dest(mp + "w2", L.w2, HD, s.low_rank, 0);
+      L.w0 = take(HD); dest(mp + "w0", L.w0, 1, HD, 0);
+      L.a_b = take(HD); dest(mp + "a.b", L.a_b, 1, HD, 0);
+      L.onorm = take(HD); dest(mp + "norm", L.onorm, 1, HD, 0);
+      L.wo = take((size_t)D * HD); dest(mp + "o", L.wo, D, HD, 0);
       L.state_off = e->state_floats;
       e->state_floats += (size_t)s.heads * s.dim * s.dim;
       e->max_hd = std::max(e->max_hd, HD);
@@ -270,7 +319,16 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
       REQUIRE(dv >= 1 && dv <= 256 && dk <= 1024, "layer %d: attention sizes dim %d (<= 1024) / vdim %d (1..256)", li, dk, dv);
       REQUIRE(s.window >= 0 && s.chunk >= 0 && s.softcap >= 0.f, "layer %d: negative window, chunk or softcap", li);
       REQUIRE(s.out_gate >= 0 && s.out_gate <= 2, "layer %d: unknown output gate %d", li, s.out_gate);
-      REQUIRE(s.qk_norm >= XOTB200_LM_QKNORM_NONE && s.qk_norm <= XOTB200_LM_QKNORM_ROW, "layer %d: unknown query/key norm %d", li, s.qk_norm);
+      REQUIRE(s.qk_norm >= XOTB200_LM_QKNORM_NONE && s.qk_norm <= XOTB200_LM_QKNORM_HEAD_PLAIN, "layer %d: unknown query/key norm %d", li, s.qk_norm);
+      REQUIRE(s.rot_dims >= 0 && s.rot_dims <= dk && s.rot_dims % 2 == 0, "layer %d: %d rotated entries of a head of %d", li, s.rot_dims, dk);
+      REQUIRE(s.rot_dims == 0 || (s.rot_base > 0.f && (s.rot_layout == XOTB200_LM_ROT_INTERLEAVED || s.rot_layout == XOTB200_LM_ROT_HALF)),
+              "layer %d: rotation needs a positive base and a known layout", li);
+      REQUIRE(s.rot_dims == 0 || s.qk_norm != XOTB200_LM_QKNORM_ROW, "layer %d: rotation is implemented with per-head query/key norms (or none)", li);
+      REQUIRE(s.rot_scale_factor == 0.f || (s.rot_scale_factor > 0.f && s.rot_scale_high > s.rot_scale_low && s.rot_scale_low > 0.f && s.rot_scale_original > 0.f),
+              "layer %d: frequency scaling needs factor > 0, 0 < low < high and the original length", li);
+      REQUIRE(s.keep_first >= 0 && s.pool >= 0 && !(s.keep_first > 0 && s.pool > 0), "layer %d: kept first tokens and pooled blocks exclude each other", li);
+      REQUIRE((s.keep_first == 0 && s.pool == 0) || (s.window > 0 && s.chunk == 0 && !s.dist_bias && s.rel_buckets == 0 && own),
+              "layer %d: kept first tokens / pooled blocks go with a sliding window, keys of the layer's own and no block mask or distance terms", li);
       REQUIRE(!s.out_bias || post_ln || post_rms, "layer %d: a bias of the output projection is added by the closing norm of the post-norm block forms only", li);
       REQUIRE(s.qk_norm != XOTB200_LM_QKNORM_ROW || (size_t)(H + G) * dk * 4 <= 200 * 1024,
               "layer %d: a query/key norm over the whole projection holds the row in shared memory: (heads + kv_heads) * dim <= 51200", li);
@@ -289,60 +347,61 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
         L.kv_src = li - e->cfg.start_layer;
       }
       // projection columns: q | k | v | gate   (k, v only with keys/values of its own)
-      L.c_q = 0; L.c_kk = H * dk; L.c_vv = L.c_kk + (own ? G * dk : 0); L.c_g = L.c_vv + (own ? G * dv : 0);
+      L.c_q = cb; L.c_kk = cb + H * dk; L.c_vv = L.c_kk + (own ? G * dk : 0); L.c_g = L.c_vv + (own ? G * dv : 0);
       const int ng = s.out_gate == 2 ? H * dv : s.out_gate == 1 ? H : 0;
-      L.n_in = L.c_g + ng;
-      L.w_in = take((size_t)L.n_in * D);
-      dest(p + "mix.q", L.w_in, H * dk, D, L.c_q);
-      if (own) { dest(p + "mix.k", L.w_in, G * dk, D, L.c_kk); dest(p + "mix.v", L.w_in, G * dv, D, L.c_vv); }
-      if (ng) dest(p + "mix.g", L.w_in, ng, D, L.c_g);
+      L.n_in = L.c_g + ng - cb;
+      L.w_in = shared ? w_shared : take((size_t)L.n_in * D);
+      dest(mp + "q", L.w_in, H * dk, D, L.c_q);
+      if (own) { dest(mp + "k", L.w_in, G * dk, D, L.c_kk); dest(mp + "v", L.w_in, G * dv, D, L.c_vv); }
+      if (ng) dest(mp + "g", L.w_in, ng, D, L.c_g);
       if (s.proj_bias) {
-        L.b_in = take(L.n_in);                                 // zero where a projection has no bias (the blob starts zeroed)
-        dest(p + "mix.q.b", L.b_in + L.c_q, 1, H * dk, 0);
-        if (own) { dest(p + "mix.k.b", L.b_in + L.c_kk, 1, G * dk, 0); dest(p + "mix.v.b", L.b_in + L.c_vv, 1, G * dv, 0); }
+        L.b_in = take(cb + L.n_in);                            // zero where a projection has no bias (the blob starts zeroed)
+        dest(mp + "q.b", L.b_in + L.c_q, 1, H * dk, 0);
+        if (own) { dest(mp + "k.b", L.b_in + L.c_kk, 1, G * dk, 0); dest(mp + "v.b", L.b_in + L.c_vv, 1, G * dv, 0); }
       }
-      if (s.qk_norm) {
+      if (s.qk_norm && s.qk_norm != XOTB200_LM_QKNORM_HEAD_PLAIN) {
         const bool whole = s.qk_norm == XOTB200_LM_QKNORM_ROW;
         const int nq = whole ? H * dk : dk, nk = whole ? G * dk : dk;
-        L.q_norm = take(nq); dest(p + "mix.q.norm", L.q_norm, 1, nq, 0);
-        if (own) { L.k_norm = take(nk); dest(p + "mix.k.norm", L.k_norm, 1, nk, 0); }
+        L.q_norm = take(nq); dest(mp + "q.norm", L.q_norm, 1, nq, 0);
+        if (own) { L.k_norm = take(nk); dest(mp + "k.norm", L.k_norm, 1, nk, 0); }
       }
-      if (s.out_bias) { L.o_b = take(D); dest(p + "mix.o.b", L.o_b, 1, D, 0); }
-      if (s.sink) { L.sink = take(H); dest(p + "mix.sink", L.sink, 1, H, 0); }
-      if (s.rel_buckets > 0) { L.rel = take((size_t)s.rel_buckets * H); dest(p + "mix.rel", L.rel, s.rel_buckets, H, 0); }
+      if (s.out_bias) { L.o_b = take(D); dest(mp + "o.b", L.o_b, 1, D, 0); }
+      if (s.sink) { L.sink = take(H); dest(mp + "sink", L.sink, 1, H, 0); }
+      if (s.rel_buckets > 0) { L.rel = take((size_t)s.rel_buckets * H); dest(mp + "rel", L.rel, s.rel_buckets, H, 0); }
       if (s.dist_bias) {
-        L.r1 = take(H); dest(p + "mix.r1", L.r1, 1, H, 0);
-        L.r2 = take(H); dest(p + "mix.r2", L.r2, 1, H, 0);
+        L.r1 = take(H); dest(mp + "r1", L.r1, 1, H, 0);
+        L.r2 = take(H); dest(mp + "r2", L.r2, 1, H, 0);
       }
-      L.wo = take((size_t)D * H * dv); dest(p + "mix.o", L.wo, D, H * dv, 0);
+      L.wo = take((size_t)D * H * dv); dest(mp + "o", L.wo, D, H * dv, 0);
       e->max_q = std::max(e->max_q, H * dk);
       e->max_qfull = std::max(e->max_qfull, H * dk);
       e->max_oh = std::max(e->max_oh, H * dv);
       if (dk % 8 || dv % 8 || dk > 256 || dv > 128) e->gqa_flash_fits = false;
+      if (s.keep_first > 0 || s.pool > 0) e->gqa_flash_fits = false;   // the tensor-core prompt kernel walks one stretch of token keys
     } else if (s.mixer == XOTB200_LM_MIX_GATED_DELTA) {
       const int H = s.heads, G = s.kv_heads, dk = s.dim, dv = s.vdim, C = 2 * G * dk + H * dv;
       REQUIRE(G >= 1 && H % G == 0, "layer %d: %d value heads do not divide into %d query/key heads", li, H, G);
       REQUIRE(dk <= 256 && dv >= 1 && dv <= 256, "layer %d: delta-rule head sizes %d / %d above 256", li, dk, dv);
       REQUIRE(s.conv_taps >= 1 && s.conv_taps <= 64, "layer %d: %d convolution taps (1..64)", li, s.conv_taps);
       // projection columns: q | k | v (the filtered channels, in this order) | output gate | beta | decay logit
-      L.c_r = 0; L.c_k = G * dk; L.c_v = 2 * G * dk; L.c_g = C; L.c_b = C + H * dv; L.c_a = L.c_b + H;
+      L.c_r = cb; L.c_k = cb + G * dk; L.c_v = cb + 2 * G * dk; L.c_g = cb + C; L.c_b = L.c_g + H * dv; L.c_a = L.c_b + H;
       L.conv_ch = C;
-      L.n_in = L.c_a + H;
-      L.w_in = take((size_t)L.n_in * D);
-      dest(p + "mix.q", L.w_in, G * dk, D, L.c_r);
-      dest(p + "mix.k", L.w_in, G * dk, D, L.c_k);
-      dest(p + "mix.v", L.w_in, H * dv, D, L.c_v);
-      dest(p + "mix.g", L.w_in, H * dv, D, L.c_g);
-      dest(p + "mix.b", L.w_in, H, D, L.c_b);
-      dest(p + "mix.a", L.w_in, H, D, L.c_a);
+      L.n_in = L.c_a + H - cb;
+      L.w_in = shared ? w_shared : take((size_t)L.n_in * D);
+      dest(mp + "q", L.w_in, G * dk, D, L.c_r);
+      dest(mp + "k", L.w_in, G * dk, D, L.c_k);
+      dest(mp + "v", L.w_in, H * dv, D, L.c_v);
+      dest(mp + "g", L.w_in, H * dv, D, L.c_g);
+      dest(mp + "b", L.w_in, H, D, L.c_b);
+      dest(mp + "a", L.w_in, H, D, L.c_a);
       L.conv_w = take((size_t)C * s.conv_taps);
-      dest(p + "mix.q.conv", L.conv_w, G * dk, s.conv_taps, L.c_r);
-      dest(p + "mix.k.conv", L.conv_w, G * dk, s.conv_taps, L.c_k);
-      dest(p + "mix.v.conv", L.conv_w, H * dv, s.conv_taps, L.c_v);
-      L.a_log = take(H); dest(p + "mix.A_log", L.a_log, 1, H, 0);
-      L.dt_bias = take(H); dest(p + "mix.dt_bias", L.dt_bias, 1, H, 0);
-      L.onorm = take(dv); dest(p + "mix.norm", L.onorm, 1, dv, 0);
-      L.wo = take((size_t)D * H * dv); dest(p + "mix.o", L.wo, D, H * dv, 0);
+      dest(mp + "q.conv", L.conv_w, G * dk, s.conv_taps, 0);
+      dest(mp + "k.conv", L.conv_w, G * dk, s.conv_taps, G * dk);
+      dest(mp + "v.conv", L.conv_w, H * dv, s.conv_taps, 2 * G * dk);
+      L.a_log = take(H); dest(mp + "A_log", L.a_log, 1, H, 0);
+      L.dt_bias = take(H); dest(mp + "dt_bias", L.dt_bias, 1, H, 0);
+      L.onorm = take(dv); dest(mp + "norm", L.onorm, 1, dv, 0);
+      L.wo = take((size_t)D * H * dv); dest(mp + "o", L.wo, D, H * dv, 0);
       L.state_off = e->state_floats;
       e->state_floats += (size_t)H * dk * dv;
       L.conv_off = e->state_floats;
@@ -350,14 +409,90 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
       e->max_hd = std::max(e->max_hd, H * std::max(dk, dv));
       e->max_oh = std::max(e->max_oh, H * dv);
       e->max_conv = std::max(e->max_conv, C);
+    } else if (s.mixer == XOTB200_LM_MIX_MATRIX_LSTM) {
+      const int H = s.heads, dk = s.dim, dv = s.vdim;
+      REQUIRE(dk <= 256 && dv >= 1 && dv + 1 <= 256, "layer %d: matrix-LSTM head sizes %d / %d above 256 / 255", li, dk, dv);
+      REQUIRE(s.gate_cap > 0.f, "layer %d: the gates' cap must be positive", li);
+      // projection columns: q | k | v | output gate | input-gate logits | forget-gate logits
+      L.c_r = cb; L.c_k = cb + H * dk; L.c_v = cb + 2 * H * dk; L.c_g = L.c_v + H * dv; L.c_i = L.c_g + H * dv; L.c_f = L.c_i + H;
+      L.n_in = L.c_f + H - cb;
+      L.w_in = shared ? w_shared : take((size_t)L.n_in * D);
+      dest(mp + "q", L.w_in, H * dk, D, L.c_r);
+      dest(mp + "k", L.w_in, H * dk, D, L.c_k);
+      dest(mp + "v", L.w_in, H * dv, D, L.c_v);
+      dest(mp + "g", L.w_in, H * dv, D, L.c_g);
+      dest(mp + "i", L.w_in, H, D, L.c_i);
+      dest(mp + "f", L.w_in, H, D, L.c_f);
+      L.i_b = take(H); dest(mp + "i.b", L.i_b, 1, H, 0);
+      L.f_b = take(H); dest(mp + "f.b", L.f_b, 1, H, 0);
+      L.onorm = take((size_t)H * dv); dest(mp + "norm", L.onorm, 1, H * dv, 0);
+      L.wo = take((size_t)D * H * dv); dest(mp + "o", L.wo, D, H * dv, 0);
+      L.state_off = e->state_floats;                       // per head [dk, dv + 1]: the last column is the normaliser
+      e->state_floats += (size_t)H * dk * (dv + 1);
+      L.m_off = e->state_floats;
+      e->state_floats += (size_t)H;
+      e->max_hd = std::max(e->max_hd, H * std::max(dk, dv + 1));
+      e->max_oh = std::max(e->max_oh, H * dv);
+      e->max_heads_rec = std::max(e->max_heads_rec, H);
+      e->max_vaug = std::max(e->max_vaug, H * (dv + 1));
+    } else if (s.mixer == XOTB200_LM_MIX_MAMBA2) {
+      const int H = s.heads, G = s.kv_heads, N = s.dim, dv = s.vdim, inner = H * dv, C = inner + 2 * G * N;
+      REQUIRE(G >= 1 && H % G == 0, "layer %d: %d heads do not divide into %d groups", li, H, G);
+      REQUIRE(N <= 256 && dv >= 1 && dv <= 256, "layer %d: state size %d / head size %d above 256", li, N, dv);
+      REQUIRE(s.conv_taps >= 1 && s.conv_taps <= 64, "layer %d: %d convolution taps (1..64)", li, s.conv_taps);
+      REQUIRE(s.out_norm_groups >= 1 && inner % s.out_norm_groups == 0, "layer %d: %d channels do not divide into %d norm parts", li, inner, s.out_norm_groups);
+      // projection columns as stored: z | x | B | C (x, B, C are the filtered channels) | dt
+      L.c_z = cb; L.c_v = cb + inner; L.c_k = L.c_v + inner; L.c_r = L.c_k + G * N; L.c_dt = L.c_r + G * N;
+      L.conv_ch = C;
+      L.n_in = L.c_dt + H - cb;
+      L.w_in = shared ? w_shared : take((size_t)L.n_in * D);
+      dest(mp + "in", L.w_in, L.n_in, D, cb);
+      L.conv_w = take((size_t)C * s.conv_taps); dest(mp + "conv", L.conv_w, C, s.conv_taps, 0);
+      L.conv_b = take(C); dest(mp + "conv.b", L.conv_b, 1, C, 0);
+      L.dt_bias = take(H); dest(mp + "dt_bias", L.dt_bias, 1, H, 0);
+      L.a_log = take(H); dest(mp + "A_log", L.a_log, 1, H, 0);
+      L.d_skip = take(H); dest(mp + "D", L.d_skip, 1, H, 0);
+      L.onorm = take(inner); dest(mp + "norm", L.onorm, 1, inner, 0);
+      L.wo = take((size_t)D * inner); dest(mp + "o", L.wo, D, inner, 0);
+      L.state_off = e->state_floats;
+      e->state_floats += (size_t)H * N * dv;
+      L.conv_off = e->state_floats;
+      e->state_floats += (size_t)(s.conv_taps - 1) * C;
+      e->max_hd = std::max(e->max_hd, H * std::max(N, dv));
+      e->max_oh = std::max(e->max_oh, inner);
+      e->max_conv = std::max(e->max_conv, C);
     } else {
       REQUIRE(false, "layer %d: unknown mixer kind %d", li, s.mixer);
     }
-    e->max_in = std::max(e->max_in, L.n_in);
+    return 0;
+    };
+    if (s.par_on) {
+      REQUIRE(s.mixer == XOTB200_LM_MIX_ATTENTION || s.mixer == XOTB200_LM_MIX_GATED_DELTA || s.mixer == XOTB200_LM_MIX_MATRIX_LSTM || s.mixer == XOTB200_LM_MIX_MAMBA2,
+              "layer %d: mixer kind %d cannot share a layer", li, s.mixer);
+      REQUIRE(s.par_mixer == XOTB200_LM_MIX_GATED_DELTA || s.par_mixer == XOTB200_LM_MIX_MATRIX_LSTM || s.par_mixer == XOTB200_LM_MIX_MAMBA2,
+              "layer %d: the second mixer of a layer is a recurrent one (gated delta rule, matrix LSTM, state-space), not kind %d", li, s.par_mixer);
+      LmLayer R{};
+      R.s = xotb200_lm_layer{};
+      R.s.mixer = s.par_mixer; R.s.heads = s.par_heads; R.s.kv_heads = s.par_kv_heads; R.s.dim = s.par_dim; R.s.vdim = s.par_vdim;
+      R.s.conv_taps = s.par_conv_taps; R.s.out_norm_groups = s.par_out_norm_groups; R.s.gate_cap = s.par_gate_cap; R.s.kv_from = -1;
+      REQUIRE(R.s.heads >= 1 && R.s.dim >= 1, "layer %d: heads and dim of the second mixer must be positive", li);
+      const int n_left = mixer_columns(s), n_right = mixer_columns(R.s);
+      const size_t w_all = take((size_t)(n_left + n_right) * D);   // the rows of both mixers' projections: one product
+      TRY(layout_mixer(L, p + "mix.left.", 0, true, w_all));
+      TRY(layout_mixer(R, p + "mix.right.", n_left, true, w_all));
+      REQUIRE(L.n_in == n_left && R.n_in == n_right, "internal: projection columns of layer %d", li);
+      L.ld_in = R.ld_in = n_left + n_right;
+      L.par.push_back(R);
+    } else {
+      TRY(layout_mixer(L, p + "mix.", 0, false, 0));
+      L.ld_in = L.n_in;
+    }
+    e->max_in = std::max(e->max_in, L.ld_in);
     const bool has_ff = s.ff_kind == XOTB200_LM_FF_MOE ? s.experts > 0 : s.ff > 0;
     if (has_ff) {
-      L.norm2 = take(D); dest(p + "norm2", L.norm2, 1, D, 0);
-      if (!post_rms) { L.norm2b = take(D); dest(p + "norm2" + nb, L.norm2b, 1, D, 0); }
+      L.norm2 = take(NW); dest(p + "norm2", L.norm2, 1, NW, 0);
+      if (!post_rms && !pre_scalar) { L.norm2b = take(D); dest(p + "norm2" + nb, L.norm2b, 1, D, 0); }
+      if (pre_scalar) sublayer_extras(L, p, 1);
     }
     if (s.ff_kind == XOTB200_LM_FF_MOE && has_ff) {
       const int E = s.experts, F = s.expert_ff;
@@ -394,7 +529,8 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
       e->max_eff = std::max(e->max_eff, F);
       e->max_experts = std::max(e->max_experts, E);
     } else if (has_ff) {
-      REQUIRE(s.ff_kind == XOTB200_LM_FF_RELU2 || s.ff_kind == XOTB200_LM_FF_XIELU, "layer %d: unknown feed-forward kind %d", li, s.ff_kind);
+      REQUIRE(s.ff_kind == XOTB200_LM_FF_RELU2 || s.ff_kind == XOTB200_LM_FF_XIELU || s.ff_kind == XOTB200_LM_FF_GELU, "layer %d: unknown feed-forward kind %d", li,
+              s.ff_kind);
       L.up = take((size_t)s.ff * D); dest(p + "mlp.up", L.up, s.ff, D, 0);
       L.down = take((size_t)D * s.ff); dest(p + "mlp.down", L.down, D, s.ff, 0);
       if (s.ff_kind == XOTB200_LM_FF_XIELU) { L.act_p = take(2); dest(p + "mlp.act", L.act_p, 1, 2, 0); }
@@ -403,7 +539,7 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
     e->layers.push_back(L);
   }
   if (e->last) {
-    e->final_norm = take(D); dest("final.norm", e->final_norm, 1, D, 0);
+    e->final_norm = take(NW); dest("final.norm", e->final_norm, 1, NW, 0);
     if (post_ln) { e->final_norm_b = take(D); dest("final.norm.b", e->final_norm_b, 1, D, 0); }   // a final RMS norm has a weight only
     e->head = take((size_t)V * D); dest("head", e->head, V, D, 0);
   }
@@ -583,8 +719,18 @@ static int ensure_scratch(xotb200_lm* e, int M, int n_want) {
   if (M > e->m_cap) {
     drop_graphs(e);
     const size_t m = (size_t)std::max(M, 64), z = e->esz;
-    TRY(regrow(e->x, m * D * 4));
+    TRY(regrow(e->x, m * D * 4 * (e->pre_scalar ? std::max(1, e->cfg.streams) : 1)));
     TRY(regrow(e->y, m * D * 4));
+    if (e->pre_scalar) {
+      TRY(regrow(e->y2, m * D * 4));
+      TRY(regrow(e->h0, m * D * 4));
+    }
+    if (e->max_heads_rec) {
+      TRY(regrow(e->gdec, m * e->max_heads_rec * 4));
+      TRY(regrow(e->ginw, m * e->max_heads_rec * 4));
+      TRY(regrow(e->gfloor, m * e->max_heads_rec * 4));
+      TRY(regrow(e->vaug, m * e->max_vaug * 4));
+    }
     TRY(regrow(e->proj, m * e->max_in * 4));
     TRY(regrow(e->qraw, m * e->max_q * 4));
     TRY(regrow(e->qfull, m * e->max_qfull * 4));
@@ -592,10 +738,10 @@ static int ensure_scratch(xotb200_lm* e, int M, int n_want) {
     TRY(regrow(e->oraw, m * e->max_hd * 4));
     TRY(regrow(e->du, m * e->max_hd * 4));
     TRY(regrow(e->dau, m * e->max_hd * 4));
-    if (e->max_conv) {
+    if (e->max_conv || e->max_heads_rec) {
       TRY(regrow(e->dkk, m * e->max_hd * 4));
       TRY(regrow(e->drr, m * e->max_hd * 4));
-      TRY(regrow(e->cvb, m * e->max_conv * 4));
+      TRY(regrow(e->cvb, m * std::max(1, e->max_conv) * 4));
     }
     if (e->max_top) {
       TRY(regrow(e->moe_ids, m * e->max_top * 4));
@@ -791,14 +937,14 @@ static int attention_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
 }
 
 template <int KPT, int P, int NC>
-static int launch_delta(xotb200_lm* e, LmLayer& L, const StepPlan& sp, DeltaSrc ks, DeltaSrc rs, DeltaSrc vs) {
+static int launch_delta(xotb200_lm* e, LmLayer& L, const StepPlan& sp, DeltaSrc ks, DeltaSrc rs, DeltaSrc vs, int dk, int dv, bool removal) {
   const xotb200_lm_layer& s = L.s;
   constexpr int CPW = (32 / P) * NC;
-  const int warps = std::max(1, std::min(4, cdiv(s.vdim, CPW)));
-  const dim3 grid(sp.n_seq * s.heads, cdiv(s.vdim, warps * CPW));
-  const int HD = s.heads * s.dim;
-  const int vec4 = (s.dim % 4 == 0 && s.vdim % 4 == 0 && HD % 4 == 0 && (ks.ld | ks.col | rs.ld | rs.col | vs.ld | vs.col) % 4 == 0) ? 1 : 0;
-  delta_rule_kernel<KPT, P, NC><<<grid, warps * 32, 0, e->stream>>>(ks, rs, vs, e->wlog, e->du, e->dau, sp.seqs, s.heads, s.dim, s.vdim,
+  const int warps = std::max(1, std::min(4, cdiv(dv, CPW)));
+  const dim3 grid(sp.n_seq * s.heads, cdiv(dv, warps * CPW));
+  const int HD = s.heads * dk;
+  const int vec4 = (dk % 4 == 0 && dv % 4 == 0 && HD % 4 == 0 && (ks.ld | ks.col | rs.ld | rs.col | vs.ld | vs.col) % 4 == 0) ? 1 : 0;
+  delta_rule_kernel<KPT, P, NC><<<grid, warps * 32, 0, e->stream>>>(ks, rs, vs, e->wlog, removal ? e->du : nullptr, removal ? e->dau : nullptr, sp.seqs, s.heads, dk, dv,
                                                                     e->state + L.state_off, e->state_floats, e->oraw, vec4);
   CK(cudaGetLastError());
   e->launches++;
@@ -808,20 +954,21 @@ static int launch_delta(xotb200_lm* e, LmLayer& L, const StepPlan& sp, DeltaSrc 
 // key rows over 4 or 8 lanes, few columns per thread, four warps per block.  The variant is chosen by the larger of the key and
 // value sizes; of the columns-per-thread choices the widest that still gives CTAs for three quarters of the SMs (a single prompt has only
 // heads x column groups CTAs: narrower threads mean more CTAs and more warps per scheduler to hide the dependent latency).
-static int run_delta(xotb200_lm* e, LmLayer& L, const StepPlan& sp, DeltaSrc ks, DeltaSrc rs, DeltaSrc vs) {
-  const int d = std::max(L.s.dim, L.s.vdim);
+// dk x dv: the state of a head (the mixers that ride on this kernel say what that is); removal: the rule has its - au (u^T S) term
+static int run_delta(xotb200_lm* e, LmLayer& L, const StepPlan& sp, DeltaSrc ks, DeltaSrc rs, DeltaSrc vs, int dk, int dv, bool removal) {
+  const int d = std::max(dk, dv);
   auto fills = [&](int P, int NC) {                    // CTAs of a variant against the SMs
-    const int cpw = (32 / P) * NC, warps = std::max(1, std::min(4, cdiv(L.s.vdim, cpw)));
-    return 4L * sp.n_seq * L.s.heads * cdiv(L.s.vdim, warps * cpw) >= 3L * e->sm_count;
+    const int cpw = (32 / P) * NC, warps = std::max(1, std::min(4, cdiv(dv, cpw)));
+    return 4L * sp.n_seq * L.s.heads * cdiv(dv, warps * cpw) >= 3L * e->sm_count;
   };
-  if (d <= 16) return launch_delta<4, 4, 2>(e, L, sp, ks, rs, vs);
-  if (d <= 32) return fills(4, 2) ? launch_delta<8, 4, 2>(e, L, sp, ks, rs, vs) : launch_delta<8, 4, 1>(e, L, sp, ks, rs, vs);
+  if (d <= 16) return launch_delta<4, 4, 2>(e, L, sp, ks, rs, vs, dk, dv, removal);
+  if (d <= 32) return fills(4, 2) ? launch_delta<8, 4, 2>(e, L, sp, ks, rs, vs, dk, dv, removal) : launch_delta<8, 4, 1>(e, L, sp, ks, rs, vs, dk, dv, removal);
   if (d <= 64)
-    return fills(8, 4) ? launch_delta<8, 8, 4>(e, L, sp, ks, rs, vs)
-         : fills(8, 2) ? launch_delta<8, 8, 2>(e, L, sp, ks, rs, vs)
-                       : launch_delta<8, 8, 1>(e, L, sp, ks, rs, vs);
-  if (d <= 128) return fills(8, 2) ? launch_delta<16, 8, 2>(e, L, sp, ks, rs, vs) : launch_delta<16, 8, 1>(e, L, sp, ks, rs, vs);
-  return launch_delta<32, 8, 1>(e, L, sp, ks, rs, vs);
+    return fills(8, 4) ? launch_delta<8, 8, 4>(e, L, sp, ks, rs, vs, dk, dv, removal)
+         : fills(8, 2) ? launch_delta<8, 8, 2>(e, L, sp, ks, rs, vs, dk, dv, removal)
+                       : launch_delta<8, 8, 1>(e, L, sp, ks, rs, vs, dk, dv, removal);
+  if (d <= 128) return fills(8, 2) ? launch_delta<16, 8, 2>(e, L, sp, ks, rs, vs, dk, dv, removal) : launch_delta<16, 8, 1>(e, L, sp, ks, rs, vs, dk, dv, removal);
+  return launch_delta<32, 8, 1>(e, L, sp, ks, rs, vs, dk, dv, removal);
 }
 
 template <typename T>
@@ -838,9 +985,9 @@ static int delta_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
                                                                               s.heads, s.dim, M);
   CK(cudaGetLastError());
   e->launches++;
-  TRY(run_delta(e, L, sp, DeltaSrc{e->proj, L.n_in, L.c_k}, DeltaSrc{e->proj, L.n_in, L.c_r}, DeltaSrc{e->proj, L.n_in, L.c_v}));
-  head_norm_gate_kernel<T><<<cdiv((long)M * s.heads, 8), 256, 0, e->stream>>>(e->oraw, at<T>(e, L.onorm), s.vdim, e->proj, L.n_in, L.c_g, 0, static_cast<T*>(e->oh),
-                                                                               s.heads, s.vdim, e->cfg.norm_eps, M);
+  TRY(run_delta(e, L, sp, DeltaSrc{e->proj, L.n_in, L.c_k}, DeltaSrc{e->proj, L.n_in, L.c_r}, DeltaSrc{e->proj, L.n_in, L.c_v}, s.dim, s.vdim, true));
+  head_norm_gate_kernel<T><<<cdiv((long)M * s.heads, 8), 256, 0, e->stream>>>(e->oraw, s.vdim, nullptr, at<T>(e, L.onorm), s.vdim, e->proj, L.n_in, L.c_g, 0,
+                                                                               static_cast<T*>(e->oh), s.heads, s.vdim, e->cfg.norm_eps, M);
   CK(cudaGetLastError());
   e->launches++;
   TRY((product<T, T, float, 0>(e, static_cast<T*>(e->oh), HD, 0, at<T>(e, L.wo), HD, 1, 0, e->y, D, 0, M, D, HD, 1)));
@@ -857,6 +1004,8 @@ static int gqa_key_runs(const xotb200_lm* e, const xotb200_lm_layer& s, int n_it
   int span = std::max(1, max_len);
   if (s.window > 0) span = std::min(span, s.window + qpi);
   if (s.chunk > 0) span = std::min(span, s.chunk + qpi - 1);   // an item's rows may straddle two blocks: its keys start at the first row's block
+  if (s.keep_first > 0) span += std::min(s.keep_first, std::max(1, max_len));   // extra keys in front of the token stretch
+  if (s.pool > 0) span += std::max(1, max_len) / s.pool;
   int splits = 1;
   const long ctas = (long)n_items * s.kv_heads * ytiles;
   if (ctas > 0 && ctas < e->sm_count) splits = std::max(1, std::min(std::min(32, cdiv(span, 32)), cdiv(2 * e->sm_count, ctas)));
@@ -864,35 +1013,42 @@ static int gqa_key_runs(const xotb200_lm* e, const xotb200_lm_layer& s, int n_it
   return cdiv(span, *run);
 }
 
+// (the projection of the layer's mixers is in e->proj, leading dimension L.ld_in; the mixer's output goes to yout)
 template <typename T>
-static int gqa_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
+static int gqa_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp, float* yout) {
   const xotb200_lm_layer& s = L.s;
   const int D = e->cfg.width, M = sp.M, H = s.heads, G = s.kv_heads, dk = s.dim, dv = s.vdim, rep = H / G;
   const bool own = s.kv_from < 0;
-  T* h = static_cast<T*>(e->h);
-  TRY((product<T, T, float, 0>(e, h, D, 0, at<T>(e, L.w_in), D, 1, 0, e->proj, L.n_in, 0, M, L.n_in, D, 1)));
   const Paging pg{e->d_table, e->pages_per_slot, e->page_size};
   T* pool = static_cast<T*>(e->layers[L.kv_src].pool);
   const int slots = H + (own ? 2 * G : 0);
   bf16* q16 = sp.n_gqa_tiles > 0 ? static_cast<bf16*>(e->q16) : nullptr;
+  const bool weighted = s.qk_norm == XOTB200_LM_QKNORM_HEAD || s.qk_norm == XOTB200_LM_QKNORM_ROW;
   if (s.qk_norm == XOTB200_LM_QKNORM_ROW) {
     const int nt = std::min(1024, std::max(128, cdiv(H * dk, 4 * 32) * 32));
     auto pk = gqa_prepare_row_kernel<T>;
     const size_t psm = (size_t)(H + (own ? G : 0)) * dk * 4;
     TRY(opt_in_smem(pk, psm));
-    pk<<<M, nt, psm, e->stream>>>(e->proj, L.n_in, L.c_q, L.c_kk, L.c_vv, s.proj_bias ? at<T>(e, L.b_in) : nullptr, at<T>(e, L.q_norm),
+    pk<<<M, nt, psm, e->stream>>>(e->proj, L.ld_in, L.c_q, L.c_kk, L.c_vv, s.proj_bias ? at<T>(e, L.b_in) : nullptr, at<T>(e, L.q_norm),
                                                         own ? at<T>(e, L.k_norm) : nullptr, e->cfg.norm_eps, H, G, dk, dv, own ? 1 : 0, s.q_temp_coef,
                                                         s.q_temp_every, sp.row_slot, sp.row_pos, pg, pool, e->qfull, q16);
   } else {
     gqa_prepare_kernel<T><<<cdiv((long)M * slots, 8), 256, 0, e->stream>>>(
-        e->proj, L.n_in, L.c_q, L.c_kk, L.c_vv, s.proj_bias ? at<T>(e, L.b_in) : nullptr, s.qk_norm ? at<T>(e, L.q_norm) : nullptr,
-        s.qk_norm && own ? at<T>(e, L.k_norm) : nullptr, e->cfg.norm_eps, H, G, dk, dv, own ? 1 : 0, s.q_temp_coef, s.q_temp_every, sp.row_slot, sp.row_pos,
-        pg, pool, e->qfull, q16, M);
+        e->proj, L.ld_in, L.c_q, L.c_kk, L.c_vv, s.proj_bias ? at<T>(e, L.b_in) : nullptr, weighted ? at<T>(e, L.q_norm) : nullptr,
+        weighted && own ? at<T>(e, L.k_norm) : nullptr, e->cfg.norm_eps, H, G, dk, dv, own ? 1 : 0, s.q_temp_coef, s.q_temp_every, sp.row_slot, sp.row_pos,
+        pg, pool, e->qfull, q16, M, s.qk_norm != XOTB200_LM_QKNORM_NONE ? 1 : 0, s.rot_dims > 0 ? L.freqs : nullptr, s.rot_dims, s.rot_layout);
   }
   CK(cudaGetLastError());
   e->launches++;
+  const size_t pool_rows = (size_t)e->n_pages * e->page_size;
+  if (s.pool > 0 && (sp.max_rows + s.pool - 1) / s.pool + 1 > 0) {
+    // blocks whose last token this step appended get their pooled row (after the append, before any reader)
+    gqa_pool_blocks_kernel<T><<<dim3(sp.n_seq, sp.max_rows / s.pool + 1), 128, 0, e->stream>>>(pool, pg, pool_rows, sp.seqs, s.pool, G * (dk + dv));
+    CK(cudaGetLastError());
+    e->launches++;
+  }
   const GqaScore sc{s.scale, s.softcap, s.window, s.chunk, s.dist_bias ? at<T>(e, L.r1) : nullptr, s.dist_bias ? at<T>(e, L.r2) : nullptr,
-                    s.rel_buckets > 0 ? L.rel_tab : nullptr, L.rel_n, s.sink ? at<T>(e, L.sink) : nullptr};
+                    s.rel_buckets > 0 ? L.rel_tab : nullptr, L.rel_n, s.sink ? at<T>(e, L.sink) : nullptr, s.keep_first, s.pool, pool_rows};
   const float* gate = s.out_gate ? e->proj : nullptr;
   const int qpi = gqa_rows_per_item(s);
   const auto& it = sp.items.at(-qpi);   // the lists of this mixer have negative keys
@@ -907,7 +1063,7 @@ static int gqa_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
   do {                                                                                                                                       \
     auto kern = gqa_attention_kernel<T, NACC>;                                                                                               \
     TRY(opt_in_smem(kern, smem));                                                                                                            \
-    kern<<<grid, nw * 32, smem, e->stream>>>(e->qfull, pool, pg, it.first, H, G, dk, dv, sc, gate, s.out_gate, L.n_in, L.c_g,                \
+    kern<<<grid, nw * 32, smem, e->stream>>>(e->qfull, pool, pg, it.first, H, G, dk, dv, sc, gate, s.out_gate, L.ld_in, L.c_g,               \
                                              static_cast<T*>(e->oh), run, e->part);                                                          \
   } while (0)
     if (dv <= 32) LAUNCH_GQA(1);
@@ -919,7 +1075,7 @@ static int gqa_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
     e->launches++;
     if (splits > 1) {
       gqa_combine_kernel<T><<<dim3(it.second, cdiv(qpi * H, 8)), 256, 0, e->stream>>>(e->part, it.first, H, dv, splits, s.sink ? at<T>(e, L.sink) : nullptr, gate,
-                                                                                     s.out_gate, L.n_in, L.c_g, static_cast<T*>(e->oh));
+                                                                                     s.out_gate, L.ld_in, L.c_g, static_cast<T*>(e->oh));
       CK(cudaGetLastError());
       e->launches++;
     }
@@ -945,7 +1101,7 @@ static int gqa_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
     auto kern = gqa_flash_kernel<DVT>;                                                                                                     \
     TRY(opt_in_smem(kern, fsm));                                                                                                           \
     kern<<<grid, 128, fsm, e->stream>>>(static_cast<const bf16*>(e->q16), pool, pg, sp.gqa_tiles, H, G, dk, dv, sc,                        \
-                                        s.dist_bias ? e->dist_tab : nullptr, dist_n, gate, s.out_gate, L.n_in, L.c_g, static_cast<bf16*>(e->oh)); \
+                                        s.dist_bias ? e->dist_tab : nullptr, dist_n, gate, s.out_gate, L.ld_in, L.c_g, static_cast<bf16*>(e->oh)); \
   } while (0)
       if (dvt == 8) LAUNCH_GQA_FLASH(8);
       else LAUNCH_GQA_FLASH(16);
@@ -955,37 +1111,85 @@ static int gqa_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
       e->flash_launches++;
     }
   }
-  TRY((product<T, T, float, 0>(e, static_cast<T*>(e->oh), (long)H * dv, 0, at<T>(e, L.wo), (long)H * dv, 1, 0, e->y, D, 0, M, D, H * dv, 1)));
+  TRY((product<T, T, float, 0>(e, static_cast<T*>(e->oh), (long)H * dv, 0, at<T>(e, L.wo), (long)H * dv, 1, 0, yout, D, 0, M, D, H * dv, 1)));
+  return 0;
+}
+
+// short causal convolution of C projection columns starting at col0 (filter inputs of earlier steps from the slot's state, which
+// then moves on) -> e->cvb [M, C]
+template <typename T>
+static int filter_channels(xotb200_lm* e, LmLayer& L, const StepPlan& sp, int col0, int C, const T* bias) {
+  const xotb200_lm_layer& s = L.s;
+  float* cstate = e->state + L.conv_off;
+  const int zrows = std::max(1, std::min(128, cdiv(sp.max_rows, 8)));
+  short_conv_kernel<T, float><<<dim3(sp.n_seq, cdiv(C, 256), zrows), 256, 0, e->stream>>>(e->proj, L.ld_in, col0, C, at<T>(e, L.conv_w), bias, s.conv_taps, 1, 0,
+                                                                                          sp.seqs, cstate, e->state_floats, e->cvb, C);
+  CK(cudaGetLastError());
+  e->launches++;
+  if (s.conv_taps > 1) {
+    conv_state_update_kernel<<<dim3(sp.n_seq, cdiv(C, 256)), 256, 0, e->stream>>>(e->proj, L.ld_in, col0, C, s.conv_taps, sp.seqs, cstate, e->state_floats);
+    CK(cudaGetLastError());
+    e->launches++;
+  }
   return 0;
 }
 
 template <typename T>
-static int gated_delta_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
+static int gated_delta_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp, float* yout) {
   const xotb200_lm_layer& s = L.s;
   const int D = e->cfg.width, M = sp.M, H = s.heads, G = s.kv_heads, dk = s.dim, dv = s.vdim, C = L.conv_ch;
-  T* h = static_cast<T*>(e->h);
-  TRY((product<T, T, float, 0>(e, h, D, 0, at<T>(e, L.w_in), D, 1, 0, e->proj, L.n_in, 0, M, L.n_in, D, 1)));
-  float* cstate = e->state + L.conv_off;
-  const int zrows = std::max(1, std::min(128, cdiv(sp.max_rows, 8)));
-  short_conv_silu_kernel<T><<<dim3(sp.n_seq, cdiv(C, 256), zrows), 256, 0, e->stream>>>(e->proj, L.n_in, 0, C, at<T>(e, L.conv_w), s.conv_taps, sp.seqs, cstate,
-                                                                                        e->state_floats, e->cvb);
-  CK(cudaGetLastError());
-  e->launches++;
-  if (s.conv_taps > 1) {
-    conv_state_update_kernel<<<dim3(sp.n_seq, cdiv(C, 256)), 256, 0, e->stream>>>(e->proj, L.n_in, 0, C, s.conv_taps, sp.seqs, cstate, e->state_floats);
-    CK(cudaGetLastError());
-    e->launches++;
-  }
-  gated_delta_prepare_kernel<T><<<cdiv((long)M * H, 8), 256, 0, e->stream>>>(e->cvb, C, e->proj, L.n_in, L.c_b, L.c_a, at<T>(e, L.a_log), at<T>(e, L.dt_bias), e->wlog,
+  TRY(filter_channels<T>(e, L, sp, L.c_r, C, nullptr));
+  gated_delta_prepare_kernel<T><<<cdiv((long)M * H, 8), 256, 0, e->stream>>>(e->cvb, C, e->proj, L.ld_in, L.c_b, L.c_a, at<T>(e, L.a_log), at<T>(e, L.dt_bias), e->wlog,
                                                                             e->du, e->dau, e->dkk, e->drr, H, G, dk, M);
   CK(cudaGetLastError());
   e->launches++;
-  TRY(run_delta(e, L, sp, DeltaSrc{e->dkk, H * dk, 0}, DeltaSrc{e->drr, H * dk, 0}, DeltaSrc{e->cvb, C, L.c_v}));
-  head_norm_gate_kernel<T><<<cdiv((long)M * H, 8), 256, 0, e->stream>>>(e->oraw, at<T>(e, L.onorm), 0, e->proj, L.n_in, L.c_g, 1, static_cast<T*>(e->oh), H, dv,
-                                                                       e->cfg.norm_eps, M);
+  TRY(run_delta(e, L, sp, DeltaSrc{e->dkk, H * dk, 0}, DeltaSrc{e->drr, H * dk, 0}, DeltaSrc{e->cvb, C, 2 * G * dk}, dk, dv, true));
+  head_norm_gate_kernel<T><<<cdiv((long)M * H, 8), 256, 0, e->stream>>>(e->oraw, dv, nullptr, at<T>(e, L.onorm), 0, e->proj, L.ld_in, L.c_g, 1, static_cast<T*>(e->oh),
+                                                                       H, dv, e->cfg.norm_eps, M);
   CK(cudaGetLastError());
   e->launches++;
-  TRY((product<T, T, float, 0>(e, static_cast<T*>(e->oh), (long)H * dv, 0, at<T>(e, L.wo), (long)H * dv, 1, 0, e->y, D, 0, M, D, H * dv, 1)));
+  TRY((product<T, T, float, 0>(e, static_cast<T*>(e->oh), (long)H * dv, 0, at<T>(e, L.wo), (long)H * dv, 1, 0, yout, D, 0, M, D, H * dv, 1)));
+  return 0;
+}
+
+// matrix LSTM: gates (a scan per request and head), vectors, the shared recurrence kernel on [dk, dv + 1] states, normaliser +
+// head norm + sigmoid gate, output product
+template <typename T>
+static int matrix_lstm_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp, float* yout) {
+  const xotb200_lm_layer& s = L.s;
+  const int D = e->cfg.width, M = sp.M, H = s.heads, dk = s.dim, dv = s.vdim;
+  mlstm_gates_kernel<T><<<cdiv((long)sp.n_seq * H, 4), 128, 0, e->stream>>>(e->proj, L.ld_in, L.c_i, L.c_f, at<T>(e, L.i_b), at<T>(e, L.f_b), s.gate_cap, sp.seqs, sp.n_seq, H,
+                                                                          e->state + L.m_off, e->state_floats, e->gdec, e->ginw, e->gfloor);
+  CK(cudaGetLastError());
+  mlstm_expand_kernel<<<cdiv((long)M * H, 8), 256, 0, e->stream>>>(e->proj, L.ld_in, L.c_r, L.c_k, L.c_v, e->gdec, e->ginw, e->wlog, e->dkk, e->drr, e->vaug, H, dk, dv, M);
+  CK(cudaGetLastError());
+  e->launches += 2;
+  TRY(run_delta(e, L, sp, DeltaSrc{e->dkk, H * dk, 0}, DeltaSrc{e->drr, H * dk, 0}, DeltaSrc{e->vaug, H * (dv + 1), 0}, dk, dv + 1, false));
+  head_norm_gate_kernel<T><<<cdiv((long)M * H, 8), 256, 0, e->stream>>>(e->oraw, dv + 1, e->gfloor, at<T>(e, L.onorm), dv, e->proj, L.ld_in, L.c_g, 0,
+                                                                       static_cast<T*>(e->oh), H, dv, e->cfg.norm_eps, M);
+  CK(cudaGetLastError());
+  e->launches++;
+  TRY((product<T, T, float, 0>(e, static_cast<T*>(e->oh), (long)H * dv, 0, at<T>(e, L.wo), (long)H * dv, 1, 0, yout, D, 0, M, D, H * dv, 1)));
+  return 0;
+}
+
+// state-space layer: filter + silu on [x | B | C], step sizes and decays, the shared recurrence kernel, skip + gate + grouped norm,
+// output product
+template <typename T>
+static int mamba2_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp, float* yout) {
+  const xotb200_lm_layer& s = L.s;
+  const int D = e->cfg.width, M = sp.M, H = s.heads, G = s.kv_heads, N = s.dim, dv = s.vdim, C = L.conv_ch, inner = H * dv;
+  TRY(filter_channels<T>(e, L, sp, L.c_v, C, at<T>(e, L.conv_b)));
+  mamba2_prepare_kernel<T><<<cdiv((long)M * H, 8), 256, 0, e->stream>>>(e->cvb, C, e->proj, L.ld_in, L.c_dt, at<T>(e, L.a_log), at<T>(e, L.dt_bias), e->wlog, e->dkk, e->drr,
+                                                                       H, G, N, dv, M);
+  CK(cudaGetLastError());
+  e->launches++;
+  TRY(run_delta(e, L, sp, DeltaSrc{e->dkk, H * N, 0}, DeltaSrc{e->drr, H * N, 0}, DeltaSrc{e->cvb, C, 0}, N, dv, false));
+  mamba2_out_kernel<T><<<cdiv((long)M * s.out_norm_groups, 8), 256, 0, e->stream>>>(e->oraw, e->cvb, C, e->proj, L.ld_in, L.c_z, at<T>(e, L.d_skip), at<T>(e, L.onorm), H, dv,
+                                                                                   s.out_norm_groups, e->cfg.norm_eps, static_cast<T*>(e->oh), M);
+  CK(cudaGetLastError());
+  e->launches++;
+  TRY((product<T, T, float, 0>(e, static_cast<T*>(e->oh), (long)inner, 0, at<T>(e, L.wo), (long)inner, 1, 0, yout, D, 0, M, D, inner, 1)));
   return 0;
 }
 
@@ -1084,7 +1288,9 @@ static int feed_forward(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
     }
     return 0;
   }
-  if (s.ff_kind == XOTB200_LM_FF_XIELU)
+  if (s.ff_kind == XOTB200_LM_FF_GELU)
+    TRY((product<T, T, T, 4>(e, h, D, 0, at<T>(e, L.up), D, 1, 0, static_cast<T*>(e->act), s.ff, 0, M, s.ff, D, 1)));
+  else if (s.ff_kind == XOTB200_LM_FF_XIELU)
     TRY((product<T, T, T, 2>(e, h, D, 0, at<T>(e, L.up), D, 1, 0, static_cast<T*>(e->act), s.ff, 0, M, s.ff, D, 1, at<T>(e, L.act_p))));
   else
     TRY((product<T, T, T, 1>(e, h, D, 0, at<T>(e, L.up), D, 1, 0, static_cast<T*>(e->act), s.ff, 0, M, s.ff, D, 1)));
@@ -1093,13 +1299,24 @@ static int feed_forward(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
 }
 
 template <typename T>
-static int run_mixer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
+static int run_branch(xotb200_lm* e, LmLayer& L, const StepPlan& sp, float* yout) {
   switch (L.s.mixer) {
-    case XOTB200_LM_MIX_LATENT_ATTN: return attention_layer<T>(e, L, sp);
-    case XOTB200_LM_MIX_DELTA_RULE: return delta_layer<T>(e, L, sp);
-    case XOTB200_LM_MIX_ATTENTION: return gqa_layer<T>(e, L, sp);
-    default: return gated_delta_layer<T>(e, L, sp);
+    case XOTB200_LM_MIX_ATTENTION: return gqa_layer<T>(e, L, sp, yout);
+    case XOTB200_LM_MIX_GATED_DELTA: return gated_delta_layer<T>(e, L, sp, yout);
+    case XOTB200_LM_MIX_MATRIX_LSTM: return matrix_lstm_layer<T>(e, L, sp, yout);
+    default: return mamba2_layer<T>(e, L, sp, yout);
   }
+}
+
+// the layer's mixer(s): h (T) -> y (fp32), and y2 for a second mixer.  Every projection that reads h — of both mixers — is one product.
+template <typename T>
+static int run_mixer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
+  if (L.s.mixer == XOTB200_LM_MIX_LATENT_ATTN) return attention_layer<T>(e, L, sp);
+  if (L.s.mixer == XOTB200_LM_MIX_DELTA_RULE) return delta_layer<T>(e, L, sp);
+  TRY((product<T, T, float, 0>(e, static_cast<T*>(e->h), e->cfg.width, 0, at<T>(e, L.w_in), e->cfg.width, 1, 0, e->proj, L.ld_in, 0, sp.M, L.ld_in, e->cfg.width, 1)));
+  TRY(run_branch<T>(e, L, sp, e->y));
+  if (!L.par.empty()) TRY(run_branch<T>(e, L.par[0], sp, e->y2));
+  return 0;
 }
 
 static void finish_logits(xotb200_lm* e, int n_want) {
@@ -1167,6 +1384,84 @@ static int run_layers_post(xotb200_lm* e, const StepPlan& sp, int n_want) {
   return 0;
 }
 
+// Pre-norm layers with one-number norm weights: x += mult * sublayer(c(rms(x) * g)), the stream kept in `streams` copies mixed by
+// hyper-connections, c(h) = h + causal convolution of h.  hc_open_kernel closes the pending sublayer and opens the next in one
+// pass; the convolution (whose inputs of earlier steps are part of a slot's state) follows as a launch of its own.
+template <typename T>
+static int run_layers_pre_scalar(xotb200_lm* e, const StepPlan& sp, int n_want) {
+  const int D = e->cfg.width, M = sp.M, S = std::max(1, e->cfg.streams), CT = e->cfg.canon_taps;
+  const bool hc = e->cfg.streams > 0;
+  const float eps = e->cfg.norm_eps, mult = e->cfg.residual_mult != 0.f ? e->cfg.residual_mult : 1.0f;
+  T* h = static_cast<T*>(e->h);
+  const int nt = std::min(1024, std::max(128, cdiv(D, 4 * 32) * 32));
+  auto okern = hc_open_kernel<T>;
+  TRY(opt_in_smem(okern, (size_t)D * 4));
+  // the pending sublayer: its output(s), their scales and its hyper-connection coefficients
+  struct Pending { const float *y = nullptr, *y2 = nullptr; float ya = 1.f, yb = 0.f; const T *mix = nullptr, *out = nullptr; } pend;
+  // closes the pending sublayer; then, with a norm weight g, opens sublayer q of layer L (h <- c(norm(u))), else writes the sum of the copies to `sum_out`
+  auto open = [&](LmLayer* L, int q, float* sum_out) -> int {
+    if (!pend.y && !L && !sum_out) return 0;
+    const T* g = L ? at<T>(e, q ? L->norm2 : L->norm1) : nullptr;
+    const T* inc = L && hc ? at<T>(e, L->hc_in[q]) : nullptr;
+    const bool conv = L && CT > 0;
+    okern<<<M, nt, (size_t)D * 4, e->stream>>>(e->x, S, pend.y, pend.y2, pend.ya, pend.yb, mult, pend.mix, pend.out, inc, g, eps, nullptr,
+                                               L ? (conv ? e->h0 : nullptr) : sum_out, L && !conv ? h : nullptr, D);
+    CK(cudaGetLastError());
+    e->launches++;
+    pend = Pending{};
+    if (conv) {
+      float* cstate = e->state + L->canon_off[q];
+      const int zrows = std::max(1, std::min(128, cdiv(sp.max_rows, 8)));
+      short_conv_kernel<T, T><<<dim3(sp.n_seq, cdiv(D, 256), zrows), 256, 0, e->stream>>>(e->h0, D, 0, D, at<T>(e, L->canon[q]), nullptr, CT, 0, 1, sp.seqs, cstate,
+                                                                                          e->state_floats, h, D);
+      CK(cudaGetLastError());
+      e->launches++;
+      if (CT > 1) {
+        conv_state_update_kernel<<<dim3(sp.n_seq, cdiv(D, 256)), 256, 0, e->stream>>>(e->h0, D, 0, D, CT, sp.seqs, cstate, e->state_floats);
+        CK(cudaGetLastError());
+        e->launches++;
+      }
+    }
+    return 0;
+  };
+  if (e->first) {
+    embed_streams_kernel<T><<<M, nt, 0, e->stream>>>(at<T>(e, e->embed), sp.tokens, e->cfg.embed_norm ? at<T>(e, e->embed_norm) : nullptr, eps, e->x, S, D);
+    CK(cudaGetLastError());
+    e->launches++;
+  }
+  for (size_t li = 0; li < e->layers.size(); ++li) {
+    LmLayer& L = e->layers[li];
+    TRY(open(&L, 0, nullptr));
+    TRY(run_mixer<T>(e, L, sp));
+    pend.y = e->y;
+    pend.ya = L.s.mix_scale != 0.f ? L.s.mix_scale : 1.0f;
+    if (!L.par.empty()) { pend.y2 = e->y2; pend.yb = L.s.par_scale; }
+    if (hc) { pend.mix = at<T>(e, L.hc_mix[0]); pend.out = at<T>(e, L.hc_out[0]); }
+    if (layer_has_ff(L.s)) {
+      TRY(open(&L, 1, nullptr));
+      TRY(feed_forward<T>(e, L, sp));
+      pend.y = e->y;
+      if (hc) { pend.mix = at<T>(e, L.hc_mix[1]); pend.out = at<T>(e, L.hc_out[1]); }
+    }
+    if (e->trace) TRY(open(nullptr, 0, e->trace_buf + li * (size_t)M * D));
+  }
+  if (e->trace) e->trace_floats = e->layers.size() * (size_t)M * D;
+  if (e->last && n_want > 0) {
+    // the final norm of the wanted rows closes the last sublayer for them on the way (the other rows' streams are not needed again)
+    T* hw = static_cast<T*>(e->hw);
+    okern<<<n_want, nt, (size_t)D * 4, e->stream>>>(e->x, S, pend.y, pend.y2, pend.ya, pend.yb, mult, pend.mix, pend.out, nullptr, at<T>(e, e->final_norm), eps, sp.want,
+                                                    nullptr, hw, D);
+    CK(cudaGetLastError());
+    e->launches++;
+    TRY((product<T, T, float, 0>(e, hw, D, 0, at<T>(e, e->head), D, 1, 0, e->logits, e->cfg.vocab, 0, n_want, e->cfg.vocab, D, 1)));
+    finish_logits(e, n_want);
+    CK(cudaGetLastError());
+  } else if (!e->last) {
+    TRY(open(nullptr, 0, e->h0));                      // a later shard continues from the summed stream
+  }
+  return 0;
+}
+
 // threads of a row's norm block: about one warp per 256 elements, at least one warp per part while parts <= 32, at most 1024
 static int norm_threads(int D, int G) {
   int nw = std::max(1, std::min(32, D / 256));
@@ -1176,6 +1471,7 @@ static int norm_threads(int D, int G) {
 
 template <typename T>
 static int run_layers(xotb200_lm* e, const StepPlan& sp, int n_want) {
+  if (e->cfg.block == XOTB200_LM_BLOCK_PRE_SCALAR) return run_layers_pre_scalar<T>(e, sp, n_want);
   if (e->cfg.block != XOTB200_LM_BLOCK_GROUP_RMS) return run_layers_post<T>(e, sp, n_want);
   const int D = e->cfg.width, G = e->cfg.norm_groups, M = sp.M;
   const float eps = e->cfg.norm_eps;
@@ -1252,12 +1548,20 @@ int xotb200_lm_create(const xotb200_lm_cfg* cfg, const xotb200_lm_layer* layers,
           "bad layer range [%d, %d] of %d", cfg->start_layer, cfg->end_layer, cfg->n_layers);
   REQUIRE(cfg->width >= 1 && cfg->vocab >= 1, "width and vocab must be positive");
   REQUIRE(cfg->norm_groups >= 1 && cfg->width % cfg->norm_groups == 0, "width %d is not a multiple of norm_groups %d", cfg->width, cfg->norm_groups);
-  REQUIRE(cfg->block == XOTB200_LM_BLOCK_GROUP_RMS || cfg->block == XOTB200_LM_BLOCK_POST_LN || cfg->block == XOTB200_LM_BLOCK_POST_RMS,
+  REQUIRE(cfg->block == XOTB200_LM_BLOCK_GROUP_RMS || cfg->block == XOTB200_LM_BLOCK_POST_LN || cfg->block == XOTB200_LM_BLOCK_POST_RMS ||
+              cfg->block == XOTB200_LM_BLOCK_PRE_SCALAR,
           "unknown block form %d", cfg->block);
+  REQUIRE(cfg->block == XOTB200_LM_BLOCK_PRE_SCALAR || (cfg->streams == 0 && cfg->canon_taps == 0 && cfg->residual_mult == 0.f),
+          "stream copies, input convolutions and a residual multiplier belong to the pre-norm block with one-number weights");
+  REQUIRE(cfg->streams >= 0 && cfg->streams <= HC_MAX_STREAMS && cfg->canon_taps >= 0 && cfg->canon_taps <= 64, "streams 0..%d, convolution taps 0..64", HC_MAX_STREAMS);
+  REQUIRE(cfg->block != XOTB200_LM_BLOCK_PRE_SCALAR || (cfg->start_layer == 0 && cfg->end_layer == cfg->n_layers - 1),
+          "a model whose stream is kept in several copies runs as one shard");
   REQUIRE(cfg->max_positions >= 0, "negative max_positions");
   REQUIRE(cfg->block != XOTB200_LM_BLOCK_GROUP_RMS || (!cfg->pos_sinusoid && !cfg->embed_norm),
-          "a computed position vector and a norm on the embedding belong to the post-norm block forms");
-  REQUIRE(!cfg->embed_norm || cfg->block == XOTB200_LM_BLOCK_POST_RMS, "the norm on the embedding is the RMS norm of the post-RMS block form");
+          "a computed position vector and a norm on the embedding belong to the other block forms");
+  REQUIRE(cfg->block != XOTB200_LM_BLOCK_PRE_SCALAR || (!cfg->pos_sinusoid && cfg->max_positions == 0), "the one-number pre-norm block form adds no position vector");
+  REQUIRE(!cfg->embed_norm || cfg->block == XOTB200_LM_BLOCK_POST_RMS || cfg->block == XOTB200_LM_BLOCK_PRE_SCALAR,
+          "the norm on the embedding is the RMS norm of the post-RMS or the one-number pre-norm block form");
   REQUIRE(!cfg->pos_sinusoid || cfg->sinusoid_base > 0.f, "the computed position vector needs a positive base");
   REQUIRE(cfg->logit_softcap >= 0.f, "negative logit soft cap");
   int ndev = 0;
@@ -1290,9 +1594,19 @@ int xotb200_lm_create(const xotb200_lm_cfg* cfg, const xotb200_lm_layer* layers,
   cudaMemsetAsync(e->d_err, 0, 4, e->stream);
   *e->h_err = 0;
   for (auto& L : e->layers) {
-    if (L.s.mixer != XOTB200_LM_MIX_LATENT_ATTN || L.s.rot_dims == 0) continue;
+    if ((L.s.mixer != XOTB200_LM_MIX_LATENT_ATTN && L.s.mixer != XOTB200_LM_MIX_ATTENTION) || L.s.rot_dims == 0) continue;
     std::vector<float> f(L.s.rot_dims / 2);
-    for (int i = 0; i < L.s.rot_dims / 2; ++i) f[i] = (float)pow((double)L.s.rot_base, -2.0 * i / L.s.rot_dims);
+    for (int i = 0; i < L.s.rot_dims / 2; ++i) {
+      double fi = pow((double)L.s.rot_base, -2.0 * i / L.s.rot_dims);
+      if (L.s.mixer == XOTB200_LM_MIX_ATTENTION && L.s.rot_scale_factor > 0.f) {
+        // long wavelengths are stretched by `factor`, short ones stay, the band between is blended by where the wavelength lies in it
+        const double orig = L.s.rot_scale_original, lo = L.s.rot_scale_low, hi = L.s.rot_scale_high, fac = L.s.rot_scale_factor;
+        const double wl = 2.0 * M_PI / fi;
+        if (wl > orig / lo) fi = fi / fac;
+        else if (wl >= orig / hi) { const double sm = (orig / wl - lo) / (hi - lo); fi = (1.0 - sm) * fi / fac + sm * fi; }
+      }
+      f[i] = (float)fi;
+    }
     if (cudaMalloc(&L.freqs, f.size() * 4) != cudaSuccess ||
         cudaMemcpyAsync(L.freqs, f.data(), f.size() * 4, cudaMemcpyHostToDevice, e->stream) != cudaSuccess ||
         cudaStreamSynchronize(e->stream) != cudaSuccess) {
@@ -1363,7 +1677,7 @@ int xotb200_lm_destroy(xotb200_lm* e) {
     if (L.rel_bucket) cudaFree(L.rel_bucket);
     if (L.rel_tab) cudaFree(L.rel_tab);
   }
-  void* ptrs[] = {e->pos_freqs, e->dist_tab, e->moe_xg, e->moe_yg, e->moe_plan, e->dkk, e->drr, e->cvb, e->moe_ids, e->moe_wts, e->mact, e->du, e->dau, e->part, e->q16, e->cbuf, e->knx, e->vxx, e->blob, e->d_stage, e->x, e->y, e->proj, e->qraw, e->qfull, e->wlog, e->oraw, e->logits, e->h, e->cqn, e->qn, e->olat, e->oh, e->act,
+  void* ptrs[] = {e->y2, e->h0, e->gdec, e->ginw, e->gfloor, e->vaug, e->pos_freqs, e->dist_tab, e->moe_xg, e->moe_yg, e->moe_plan, e->dkk, e->drr, e->cvb, e->moe_ids, e->moe_wts, e->mact, e->du, e->dau, e->part, e->q16, e->cbuf, e->knx, e->vxx, e->blob, e->d_stage, e->x, e->y, e->proj, e->qraw, e->qfull, e->wlog, e->oraw, e->logits, e->h, e->cqn, e->qn, e->olat, e->oh, e->act,
                   e->th, e->hw, e->d_argmax, e->trace_buf};
   for (void* p : ptrs)
     if (p) cudaFree(p);
@@ -1490,8 +1804,9 @@ int xotb200_lm_load_dir(xotb200_lm* e, const char* dir) {
       for (int64_t v : en.shape) n *= v;
       if (en.dtype != "BF16") { set_err("tensor '%s': dtype %s, expected BF16", it->first.c_str(), en.dtype.c_str()); rc = XOTB200_ESTRICT; break; }
       if (en.begin < 0 || en.end > data_len || en.end - en.begin != n * 2) { set_err("tensor '%s': inconsistent data_offsets", it->first.c_str()); rc = XOTB200_EIO; break; }
-      if (en.shape.empty() || en.shape.size() > 2) { set_err("tensor '%s': %zu dimensions", it->first.c_str(), en.shape.size()); rc = XOTB200_ESTRICT; break; }
-      rc = xotb200_lm_load_tensor(e, it->first.c_str(), data + en.begin, en.shape.data(), (int)en.shape.size());
+      if (en.shape.size() > 2) { set_err("tensor '%s': %zu dimensions", it->first.c_str(), en.shape.size()); rc = XOTB200_ESTRICT; break; }
+      const int64_t one = 1;                               // a tensor without dimensions is one number
+      rc = xotb200_lm_load_tensor(e, it->first.c_str(), data + en.begin, en.shape.empty() ? &one : en.shape.data(), en.shape.empty() ? 1 : (int)en.shape.size());
     }
     munmap(const_cast<char*>(base), sb.st_size);
     if (rc < 0) return rc;
@@ -1518,7 +1833,8 @@ int xotb200_lm_begin(xotb200_lm* e, int max_tokens, int max_requests, int page_s
     if (L.s.mixer == XOTB200_LM_MIX_LATENT_ATTN) row = (size_t)L.s.kv_rank + L.s.rot_dim;
     else if (L.s.mixer == XOTB200_LM_MIX_ATTENTION && L.s.kv_from < 0) row = (size_t)L.s.kv_heads * (L.s.dim + L.s.vdim);
     if (!row) continue;
-    const size_t bytes = (size_t)e->n_pages * P * row * e->esz;
+    // a layer with pooled blocks keeps them in a second half of the same geometry (block b where token b lives in the first half)
+    const size_t bytes = (size_t)e->n_pages * P * row * e->esz * (L.s.mixer == XOTB200_LM_MIX_ATTENTION && L.s.pool > 0 ? 2 : 1);
     CK(cudaMalloc(&L.pool, bytes));
     CK(cudaMemsetAsync(L.pool, 0, bytes, e->stream));
   }

@@ -138,29 +138,33 @@ __global__ void residual_rmsnorm_kernel(float* __restrict__ x, const float* __re
 }
 
 // ---------------------------------------------------------------------------------------------------------------------------
-// Short causal convolution + silu on C channels of a projection output:
-//   out[m, c] = silu( sum_{i < taps} w[c, i] * in(pos_m - (taps - 1 - i), c) )
-// in(p, c) is the projection of the request's token at position p: a row of this step when p >= the step's first position of the
-// request, else one of the last taps-1 inputs of earlier steps, kept per slot in `state` ([taps - 1][C] fp32, zero at the start
-// of a request, so positions before 0 read as zero).  grid (requests, ceil(C / 256), row lanes).
-// conv_state_update_kernel then moves the window: it must run after every reader of the old state.
+// Short causal convolution on C channels of an fp32 matrix (a projection output, or a normed sublayer input):
+//   out[m, c] = act( bias[c] + sum_{i < taps} w[c, i] * in(pos_m - (taps - 1 - i), c) )  (+ in(pos_m, c) when `residual`)
+// act: 0 none, 1 silu.  in(p, c) is the input of the request's token at position p: a row of this step when p >= the step's first
+// position of the request, else one of the last taps-1 inputs of earlier steps, kept per slot in `state` ([taps - 1][C] fp32, zero
+// at the start of a request, so positions before 0 read as zero).  TO = float or the storage type (the operand of a product).
+// grid (requests, ceil(C / 256), row lanes).  conv_state_update_kernel then moves the window: it must run after every reader of
+// the old state.
 // ---------------------------------------------------------------------------------------------------------------------------
-template <typename T>
-__global__ void short_conv_silu_kernel(const float* __restrict__ proj, int ld, int col0, int C, const T* __restrict__ w, int taps,
-                                       const Item* __restrict__ seqs, const float* __restrict__ state, size_t state_slot_stride,
-                                       float* __restrict__ out) {
+template <typename T, typename TO>
+__global__ void short_conv_kernel(const float* __restrict__ proj, int ld, int col0, int C, const T* __restrict__ w, const T* __restrict__ bias, int taps,
+                                  int act, int residual, const Item* __restrict__ seqs, const float* __restrict__ state, size_t state_slot_stride,
+                                  TO* __restrict__ out, int ld_out) {
   const Item sq = seqs[blockIdx.x];
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= C) return;
   const float* st = state + (size_t)sq.slot * state_slot_stride;
+  const float b = bias ? ldf(bias + c) : 0.f;
   for (int t = blockIdx.z; t < sq.n_rows; t += gridDim.z) {
-    float acc = 0.f;
+    float acc = b;
     for (int i = 0; i < taps; ++i) {
       const int back = taps - 1 - i, src = t - back;           // row of this step, or (negative) before it
       const float v = src >= 0 ? proj[(size_t)(sq.row0 + src) * ld + col0 + c] : st[(size_t)(src + taps - 1) * C + c];
       acc = fmaf(ldf(w + (size_t)c * taps + i), v, acc);
     }
-    out[(size_t)(sq.row0 + t) * C + c] = siluf_(acc);
+    if (act == 1) acc = siluf_(acc);
+    if (residual) acc += proj[(size_t)(sq.row0 + t) * ld + col0 + c];
+    stf(out + (size_t)(sq.row0 + t) * ld_out + c, acc);
   }
 }
 __global__ void conv_state_update_kernel(const float* __restrict__ proj, int ld, int col0, int C, int taps, const Item* __restrict__ seqs,
@@ -596,6 +600,95 @@ __global__ void moe_combine_kernel(const float* __restrict__ yg, const int* __re
     float acc = 0.f;
     for (int k = 0; k < top; ++k) acc = fmaf(wts[m * top + k], yg[(size_t)place[m * top + k] * D + d], acc);
     y[m * D + d] = accumulate ? y[m * D + d] + acc : acc;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Pre-norm block with one-number norm weights and hyper-connections (XOTB200_LM_BLOCK_PRE_SCALAR).
+// The stream of row m is kept in S copies X[m][s][:] (S = 1: the plain residual stream).
+//
+// embed_streams_kernel:  e = embed[token]; e <- e / sqrt(mean(e^2) + eps) * g; every copy starts as e.
+//
+// hc_open_kernel closes the pending sublayer and opens the next in one pass over the row:
+//   close (y != NULL):  X_t <- sum_s mix[s, t] X_s + mult * out[t] * (ya * y + yb * y2)    for all t at once   (mix, out NULL: X += ...)
+//   open              :  u = sum_s in[s] X_s  (in NULL: the sum of the copies);
+//                        with g: h = u / sqrt(mean(u^2) + eps) * g  -> out_f32 (fp32; a convolution follows) or out_t (a product follows);
+//                        without g: u itself -> out_f32 (the model's stream after a layer).
+// src_rows != NULL gathers (the final norm of the rows whose logits are wanted): row m reads X row src_rows[m]; the closed copies
+// are then not written back (the stream is not needed again).  One block per row; dynamic shared memory: D floats.  S <= 8.
+// ---------------------------------------------------------------------------------------------------------------------------
+constexpr int HC_MAX_STREAMS = 8;
+
+template <typename T>
+__global__ void embed_streams_kernel(const T* __restrict__ embed, const int* __restrict__ tokens, const T* __restrict__ g, float eps, float* __restrict__ X,
+                                     int S, int D) {
+  __shared__ float red[32];
+  const int m = blockIdx.x;
+  const T* src = embed + (size_t)tokens[m] * D;
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) { const float v = ldf(src + d); ss = fmaf(v, v, ss); }
+  const float r = 1.0f / sqrtf(block_sum(ss, red) / (float)D + eps) * (g ? ldf(g) : 1.0f);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    const float v = ldf(src + d) * r;
+    for (int s = 0; s < S; ++s) X[((size_t)m * S + s) * D + d] = v;
+  }
+}
+
+template <typename T>
+__global__ void hc_open_kernel(float* __restrict__ X, int S, const float* __restrict__ y, const float* __restrict__ y2, float ya, float yb, float mult,
+                               const T* __restrict__ mix, const T* __restrict__ outc, const T* __restrict__ inc, const T* __restrict__ g, float eps,
+                               const int* __restrict__ src_rows, float* __restrict__ out_f32, T* __restrict__ out_t, int D) {
+  extern __shared__ float hc_row[];
+  __shared__ float red[32];
+  __shared__ float c_mix[HC_MAX_STREAMS * HC_MAX_STREAMS], c_out[HC_MAX_STREAMS], c_in[HC_MAX_STREAMS];
+  const int m = blockIdx.x;
+  const size_t xm = src_rows ? src_rows[m] : m;
+  if (threadIdx.x < S * S) c_mix[threadIdx.x] = mix ? ldf(mix + threadIdx.x) : (threadIdx.x / S == threadIdx.x % S ? 1.f : 0.f);
+  if (threadIdx.x < S) {
+    c_out[threadIdx.x] = (outc ? ldf(outc + threadIdx.x) : 1.f) * mult;
+    c_in[threadIdx.x] = inc ? ldf(inc + threadIdx.x) : 1.f;
+  }
+  __syncthreads();
+  float* xr = X + xm * S * D;
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float xs[HC_MAX_STREAMS];
+#pragma unroll
+    for (int s = 0; s < HC_MAX_STREAMS; ++s) xs[s] = s < S ? xr[(size_t)s * D + d] : 0.f;
+    if (y) {
+      const float yv = ya * y[xm * D + d] + (y2 ? yb * y2[xm * D + d] : 0.f);
+      float nx[HC_MAX_STREAMS];
+#pragma unroll
+      for (int t = 0; t < HC_MAX_STREAMS; ++t) {
+        float a = 0.f;
+        if (t < S) {
+#pragma unroll
+          for (int s = 0; s < HC_MAX_STREAMS; ++s)
+            if (s < S) a = fmaf(c_mix[s * S + t], xs[s], a);
+          a = fmaf(c_out[t], yv, a);
+        }
+        nx[t] = a;
+      }
+#pragma unroll
+      for (int t = 0; t < HC_MAX_STREAMS; ++t) {
+        xs[t] = nx[t];
+        if (t < S && !src_rows) xr[(size_t)t * D + d] = nx[t];
+      }
+    }
+    float u = 0.f;
+#pragma unroll
+    for (int s = 0; s < HC_MAX_STREAMS; ++s)
+      if (s < S) u = fmaf(c_in[s], xs[s], u);
+    hc_row[d] = u;
+    ss = fmaf(u, u, ss);
+  }
+  if (!out_f32 && !out_t) return;
+  float r = 1.0f;
+  if (g) r = 1.0f / sqrtf(block_sum(ss, red) / (float)D + eps) * ldf(g);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {       // every thread reads back what it wrote
+    const float v = hc_row[d] * r;
+    if (out_f32) out_f32[(size_t)m * D + d] = v;
+    if (out_t) stf(out_t + (size_t)m * D + d, v);
   }
 }
 

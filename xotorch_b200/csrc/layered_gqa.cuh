@@ -10,10 +10,15 @@
 //                 -> + rel[a][min(i - j, rel_n - 1)]      when the layer has a learned bias per distance bucket (tabulated per
 //                                                         distance; from rel_n - 1 on every distance is in the last bucket)
 //   visible     : j <= i,  i - j < window (window > 0),  floor(i / chunk) == floor(j / chunk) (chunk > 0; blocks are counted from
-//                 position 0 of the request, whatever portion of it a step brings)
+//                 position 0 of the request, whatever portion of it a step brings);
+//                 keep_first > 0: the first keep_first tokens stay visible beyond the window;
+//                 pool > 0: every block of `pool` tokens that ends at or before i - window is seen as ONE key / value, the means of
+//                 its cached keys / values (made by gqa_pool_blocks_kernel when the block's last token is appended; they live in
+//                 the second half of the layer's pool, block b of a request at the place token b has in the first half)
 //   weights     = softmax over the visible keys (fp32); with a sink the denominator also holds exp(sink[a]), a term that has no
 //                 key, no value, no scale and no bias and counts once; output = sum_j p_j v_j, times sigmoid(gate) per head or
 //                 per entry.
+// Queries and keys may be rotated by position before they are used / cached (first rot_dims entries of a head, fp32 angle).
 // Queries may carry a temperature: the query at position p is multiplied by 1 + coef * ln(1 + (p + 1) / every), integer quotient.
 //
 // Kernels: gqa_prepare_kernel (bias, per-head RMS norm, temperature, cache append), gqa_prepare_row_kernel (the same with ONE norm
@@ -33,7 +38,20 @@ struct GqaScore {
   const float* rel;  // [H][rel_n] fp32: learned bias per distance, the last entry for every larger distance; NULL = none
   int rel_n;
   const void* sink;  // per query head, T; NULL = no sink
+  int keep_first;    // > 0: the first tokens of a request that every later row sees
+  int pool;          // > 0: tokens per pooled block
+  size_t pool_rows;  // rows of the pool's first half (token rows); pooled block b of a request lives at pool_rows + row(slot, b)
 };
+
+// Keys a work item meets come in two stretches: `extra` keys in front (kept first tokens that lie before the item's token range, or
+// the pooled blocks its last row sees), then the tokens first .. last.  A VIRTUAL index v runs over both: v < extra -> extra key v.
+__device__ __host__ __forceinline__ int gqa_extra_keys(int first, int pos_last, int window, int keep_first, int pool) {
+  if (keep_first > 0) return keep_first < first ? keep_first : first;
+  if (pool > 0 && window > 0) return pos_last - window + 1 > 0 ? (pos_last - window + 1) / pool : 0;
+  return 0;
+}
+// pooled blocks the row at `pos` sees: those with (b + 1) * pool <= pos - window + 1
+__device__ __forceinline__ int gqa_blocks_seen(int pos, int window, int pool) { return pos - window + 1 > 0 ? (pos - window + 1) / pool : 0; }
 
 // multiplier of the query at position pos (1 when coef == 0)
 __device__ __forceinline__ float gqa_query_temperature(float coef, int every, int pos) {
@@ -65,8 +83,8 @@ __device__ __forceinline__ float gqa_adjust_fast(float dot, const GqaScore& sc, 
   if (dist_bias) s += dist_bias[dist];                         // learned bias - r1 * ln(1 + r2 * distance), staged per tile; the caller's index
   return s;
 }
-__device__ __forceinline__ bool gqa_visible(int pos, int j, int window, int chunk) {
-  return j <= pos && (window == 0 || pos - j < window) && (chunk == 0 || j / chunk == pos / chunk);
+__device__ __forceinline__ bool gqa_visible(int pos, int j, int window, int chunk, int keep_first = 0) {
+  return j <= pos && (window == 0 || pos - j < window || j < keep_first) && (chunk == 0 || j / chunk == pos / chunk);
 }
 // first key any row of positions pos0 .. can see
 __device__ __host__ __forceinline__ int gqa_first_key(int pos0, int window, int chunk) {
@@ -80,14 +98,17 @@ __device__ __host__ __forceinline__ int gqa_first_key(int pos0, int window, int 
 // After the input projection: proj[m, :] (fp32) holds q (H * dk) at col_q and, for a layer with keys/values of its own, k (G * dk)
 // at col_k and v (G * dv) at col_v.  Adds the projection biases, RMS-norms every query and key head over dk (weight of size dk
 // shared by the heads; w == NULL: no norm) and stores queries as fp32 [M, H, dk] (+ a bf16 copy for the tensor-core kernel) and
-// keys / values into the row's place of the paged pool; queries are multiplied by their temperature.  One warp per (row, head
-// slot): slots 0..H-1 queries, H..H+G-1 keys, H+G..H+2G-1 values.
+// keys / values into the row's place of the paged pool; queries are multiplied by their temperature.  norm_on without weights: the
+// heads are only divided by their root mean square.  freqs != NULL: after the norm, the first rot_dims entries of every query and key
+// head are rotated by angle pos * freqs[i] (rot_layout 1: entry i pairs with i + rot_dims / 2; 0: entries 2i, 2i + 1):
+// (u, v) -> (u cos - v sin, v cos + u sin).  One warp per (row, head slot): slots 0..H-1 queries, H..H+G-1 keys, H+G..H+2G-1 values.
 // ---------------------------------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void gqa_prepare_kernel(const float* __restrict__ proj, int ld, int col_q, int col_k, int col_v, const T* __restrict__ bias,
                                    const T* __restrict__ q_norm, const T* __restrict__ k_norm, float eps, int H, int G, int dk, int dv, int own_kv,
                                    float q_temp_coef, int q_temp_every, const int* __restrict__ row_slot, const int* __restrict__ row_pos, Paging pg,
-                                   T* __restrict__ pool, float* __restrict__ qf, bf16* __restrict__ q16, int M) {
+                                   T* __restrict__ pool, float* __restrict__ qf, bf16* __restrict__ q16, int M, int norm_on,
+                                   const float* __restrict__ freqs, int rot_dims, int rot_layout) {
   const int slots = H + (own_kv ? 2 * G : 0);
   const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (idx >= M * slots) return;
@@ -104,10 +125,19 @@ __global__ void gqa_prepare_kernel(const float* __restrict__ proj, int ld, int c
   const T* w = is_q ? q_norm : k_norm;
   float ss = 0.f;
   for (int d = lane; d < dk; d += 32) { const float v = pr[c0 + d] + (bias ? ldf(bias + c0 + d) : 0.f); ss = fmaf(v, v, ss); }
-  const float rs = (w ? 1.0f / sqrtf(warp_sum(ss) / (float)dk + eps) : 1.0f) * (is_q ? gqa_query_temperature(q_temp_coef, q_temp_every, row_pos[m]) : 1.0f);
+  const float rs = (norm_on ? 1.0f / sqrtf(warp_sum(ss) / (float)dk + eps) : 1.0f) * (is_q ? gqa_query_temperature(q_temp_coef, q_temp_every, row_pos[m]) : 1.0f);
   T* kdst = is_q ? nullptr : pool + pg.row(row_slot[m], row_pos[m]) * (size_t)(G * (dk + dv)) + (size_t)hd * dk;
+  const float fpos = (float)row_pos[m];
+  const int half = rot_dims >> 1;
   for (int d = lane; d < dk; d += 32) {
-    const float v = (pr[c0 + d] + (bias ? ldf(bias + c0 + d) : 0.f)) * rs * (w ? ldf(w + d) : 1.f);
+    float v = (pr[c0 + d] + (bias ? ldf(bias + c0 + d) : 0.f)) * rs * (w ? ldf(w + d) : 1.f);
+    if (freqs && d < rot_dims) {
+      const bool lo = rot_layout ? d < half : (d & 1) == 0;   // the pair's first member
+      const int dp = rot_layout ? (lo ? d + half : d - half) : (d ^ 1), fi = rot_layout ? (lo ? d : d - half) : (d >> 1);
+      const float o = (pr[c0 + dp] + (bias ? ldf(bias + c0 + dp) : 0.f)) * rs * (w ? ldf(w + dp) : 1.f);
+      const float ang = fpos * freqs[fi], cs = cosf(ang), sn = sinf(ang);
+      v = lo ? v * cs - o * sn : v * cs + o * sn;
+    }
     if (is_q) {
       qf[((size_t)m * H + hd) * dk + d] = v;
       if (q16) q16[((size_t)m * H + hd) * dk + d] = __float2bfloat16_rn(v);
@@ -182,9 +212,29 @@ __device__ __forceinline__ float gqa_gate(const float* gate, int mode, size_t m,
 }
 
 // ---------------------------------------------------------------------------------------------------------------------------
+// Pooled blocks: when a step appends the last token of block b (tokens b * P .. b * P + P - 1) of a request, the block's pooled row
+// — the mean over its P cached rows, keys and values alike, fp32 sum — is stored at pool_rows + row(slot, b).  grid (requests of the
+// step, blocks a request can complete in it); the threads walk the row's entries.
+// ---------------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void gqa_pool_blocks_kernel(T* __restrict__ pool, Paging pg, size_t pool_rows, const Item* __restrict__ seqs, int P, int rowlen) {
+  const Item sq = seqs[blockIdx.x];
+  const int b = sq.pos0 / P + blockIdx.y;
+  if (b >= (sq.pos0 + sq.n_rows) / P) return;
+  T* dst = pool + (pool_rows + pg.row(sq.slot, b)) * (size_t)rowlen;
+  const float inv = 1.0f / (float)P;
+  for (int c = threadIdx.x; c < rowlen; c += blockDim.x) {
+    float a = 0.f;
+    for (int t = 0; t < P; ++t) a += ldf(pool + pg.row(sq.slot, b * P + t) * (size_t)rowlen + c);
+    stf(dst + c, a * inv);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
 // One CTA = one work item (up to q_per_item consecutive rows of one request) x one key/value head; one WARP owns one (row, query
 // head of the group) pair.  32 cached keys + values of the head wait in shared memory (fp32, odd row stride): lane j scores key j,
 // the softmax statistics go round by shuffles, then the lanes split the dv value columns (NACC = ceil(dv / 32) registers).
+// The keys are walked by their virtual index (extra keys first, see gqa_extra_keys).
 // gridDim.z > 1: the keys are cut into runs of `chunk_keys` (a multiple of 32); run z parks {max, sum, accumulator[dv]} in `part`
 // ([M * H][gridDim.z][2 + dv]) and gqa_combine_kernel merges them.
 // ---------------------------------------------------------------------------------------------------------------------------
@@ -213,24 +263,27 @@ __global__ void gqa_attention_kernel(const float* __restrict__ qf, const T* __re
   }
   const float r1 = sc.r1 ? ldf(static_cast<const T*>(sc.r1) + h) : 0.f, r2 = sc.r1 ? ldf(static_cast<const T*>(sc.r2) + h) : 0.f;
   const float* rel_head = sc.rel ? sc.rel + (size_t)h * sc.rel_n : nullptr;
-  int last = it.pos0 + it.n_rows - 1;
-  int first = gqa_first_key(it.pos0, sc.window, sc.chunk);
+  const int first = gqa_first_key(it.pos0, sc.window, sc.chunk), pos_last = it.pos0 + it.n_rows - 1;
+  const int extra = gqa_extra_keys(first, pos_last, sc.window, sc.keep_first, sc.pool);
+  int vfirst = 0, vlast = extra + pos_last - first;           // virtual key range of the item
   if (gridDim.z > 1) {
-    first += blockIdx.z * chunk_keys;
-    last = min(last, first + chunk_keys - 1);
+    vfirst = blockIdx.z * chunk_keys;
+    vlast = min(vlast, vfirst + chunk_keys - 1);
   }
   float acc[NACC];
 #pragma unroll
   for (int a = 0; a < NACC; ++a) acc[a] = 0.f;
   float mx = -INFINITY, den = 0.f;
   const size_t rowlen = (size_t)G * W;
-  for (int j0 = first; j0 <= last; j0 += 32) {
+  const int seen = sc.pool > 0 ? gqa_blocks_seen(pos, sc.window, sc.pool) : 0;
+  for (int j0 = vfirst; j0 <= vlast; j0 += 32) {
     __syncthreads();
     for (int jr = warp; jr < 32; jr += nw) {
-      const int j = j0 + jr;
+      const int v = j0 + jr;
       float* dst = ktile + jr * WS;
-      if (j <= last) {
-        const T* src = pool + pg.row(it.slot, j) * rowlen;
+      if (v <= vlast) {
+        const size_t prow = v >= extra ? pg.row(it.slot, first + v - extra) : sc.pool > 0 ? sc.pool_rows + pg.row(it.slot, v) : pg.row(it.slot, v);
+        const T* src = pool + prow * rowlen;
         for (int d = lane; d < dk; d += 32) dst[d] = ldf(src + (size_t)g * dk + d);
         for (int d = lane; d < dv; d += 32) dst[dk + d] = ldf(src + (size_t)G * dk + (size_t)g * dv + d);
       } else {
@@ -239,8 +292,9 @@ __global__ void gqa_attention_kernel(const float* __restrict__ qf, const T* __re
     }
     __syncthreads();
     if (!active) continue;
-    const int j = j0 + lane;
-    const bool vis = j <= last && gqa_visible(pos, j, sc.window, sc.chunk);
+    const int v = j0 + lane;
+    const int j = v >= extra ? first + v - extra : v;         // a token's position (kept first tokens keep theirs); a pooled block's index
+    const bool vis = v <= vlast && (v >= extra ? gqa_visible(pos, j, sc.window, sc.chunk, sc.keep_first) : (sc.pool > 0 ? v < seen : true));
     float s = 0.f;
     const float* kr = ktile + lane * WS;
     for (int d = 0; d < dk; ++d) s = fmaf(q[d], kr[d], s);

@@ -44,6 +44,9 @@ __device__ __forceinline__ float xielu_f(float z, float ap, float aq) {
   return z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(aq, expm1f(z) - z, 0.5f * z);
 }
 
+// the exact gelu: z (1 + erf(z / sqrt 2)) / 2
+__device__ __forceinline__ float gelu_erf_f(float z) { return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f)); }
+
 // Where a request's token lives in a paged pool: page_table[slot * pages_per_slot + pos / P] * P + pos % P.
 struct Paging {
   const int* page_table;
@@ -390,6 +393,7 @@ __device__ __forceinline__ void cp_async16(float* dst_smem, const float* src) {
 // A thread owns NC value columns x KPT key rows of the state (row i = e * P + part), so the token's vectors, read from shared
 // memory once, serve NC columns and the NC recurrences run as independent chains.  vec4: every source row is 16-byte aligned
 // (sizes and offsets multiples of 4 floats), so the staging uses 16-byte cp.async.
+// uvec == NULL: the rule has no removal term (S <- diag(w) S + k v^T): u and a * u are neither staged nor applied.
 // The write key k, the read-out vector r and the value v each come from their own fp32 matrix (pointer, leading dimension, first
 // column; head a's vector at column a * dk, resp. a * dv): a projection output or a prepared buffer.
 struct DeltaSrc {
@@ -431,6 +435,7 @@ __global__ void delta_rule_kernel(DeltaSrc ksrc, DeltaSrc rsrc, DeltaSrc vsrc, c
       const int vec = piece / perk < 5 ? piece / perk : 5, i = (piece - vec * perk) * (vec4 ? 4 : 1);
       const float* src;
       size_t stride;
+      if (!uvec && (vec == 1 || vec == 2)) continue;          // no removal term: these two stay zero
       if (vec == 0) { src = wdec + m0 * HD + h * dk + i; stride = HD; }
       else if (vec == 1) { src = auvec + m0 * HD + h * dk + i; stride = HD; }
       else if (vec == 2) { src = uvec + m0 * HD + h * dk + i; stride = HD; }
@@ -462,16 +467,18 @@ __global__ void delta_rule_kernel(DeltaSrc ksrc, DeltaSrc rsrc, DeltaSrc vsrc, c
       float dot[NC], out[NC], vj[NC];
 #pragma unroll
       for (int x = 0; x < NC; ++x) { dot[x] = 0.f; out[x] = 0.f; vj[x] = col0 + x < DKP ? b[t][5][col0 + x] : 0.f; }
+      if (uvec) {                                          // block-uniform
 #pragma unroll
-      for (int e = 0; e < KPT; ++e) {
-        const float u = b[t][2][e * P + part];
+        for (int e = 0; e < KPT; ++e) {
+          const float u = b[t][2][e * P + part];
 #pragma unroll
-        for (int x = 0; x < NC; ++x) dot[x] = fmaf(u, s[e][x], dot[x]);
+          for (int x = 0; x < NC; ++x) dot[x] = fmaf(u, s[e][x], dot[x]);
+        }
+#pragma unroll
+        for (int o = P / 2; o > 0; o >>= 1)
+#pragma unroll
+          for (int x = 0; x < NC; ++x) dot[x] += __shfl_xor_sync(0xffffffffu, dot[x], o);
       }
-#pragma unroll
-      for (int o = P / 2; o > 0; o >>= 1)
-#pragma unroll
-        for (int x = 0; x < NC; ++x) dot[x] += __shfl_xor_sync(0xffffffffu, dot[x], o);
 #pragma unroll
       for (int e = 0; e < KPT; ++e) {
         const int i = e * P + part;
@@ -504,19 +511,22 @@ __global__ void delta_rule_kernel(DeltaSrc ksrc, DeltaSrc rsrc, DeltaSrc vsrc, c
     }
 }
 
-// Output side of the delta-rule mixer: per (row, head) o / rms(o) * w_norm * sigmoid(gate) -> T, the operand of the output product.
+// Output side of the recurrent mixers: per (row, head) o / rms(o) * w_norm * sigmoid(gate) -> T, the operand of the output product.
 // w_head_stride: dv when every head has its own norm weight, 0 when the heads share one of size dv.  gate_silu: 0 = sigmoid(gate),
-// 1 = silu(gate).
+// 1 = silu(gate).  in_head_stride: entries a head holds in o_raw (dv, or dv + 1 when the entry after the values is a normaliser
+// n . q: then, with den_floor [M, H], o <- o / (max(|n . q|, den_floor) + 1e-6) before the norm).
 template <typename T>
-__global__ void head_norm_gate_kernel(const float* __restrict__ o_raw, const T* __restrict__ w_norm, int w_head_stride, const float* __restrict__ gate,
-                                      int gate_ld, int gate_col0, int gate_silu, T* __restrict__ out, int H, int dv, float eps, int M) {
+__global__ void head_norm_gate_kernel(const float* __restrict__ o_raw, int in_head_stride, const float* __restrict__ den_floor, const T* __restrict__ w_norm,
+                                      int w_head_stride, const float* __restrict__ gate, int gate_ld, int gate_col0, int gate_silu, T* __restrict__ out, int H,
+                                      int dv, float eps, int M) {
   const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (idx >= M * H) return;
   const int m = idx / H, h = idx % H;
-  const float* o = o_raw + (size_t)m * H * dv + (size_t)h * dv;
+  const float* o = o_raw + (size_t)m * H * in_head_stride + (size_t)h * in_head_stride;
+  const float pre = den_floor ? 1.0f / (fmaxf(fabsf(o[dv]), den_floor[idx]) + 1e-6f) : 1.0f;
   float s = 0.f;
-  for (int d = lane; d < dv; d += 32) s = fmaf(o[d], o[d], s);
-  const float rs = 1.0f / sqrtf(warp_sum(s) / (float)dv + eps);
+  for (int d = lane; d < dv; d += 32) { const float v = o[d] * pre; s = fmaf(v, v, s); }
+  const float rs = pre / sqrtf(warp_sum(s) / (float)dv + eps);
   for (int d = lane; d < dv; d += 32) {
     const float z = gate[(size_t)m * gate_ld + gate_col0 + h * dv + d];
     stf(out + (size_t)m * H * dv + (size_t)h * dv + d, o[d] * rs * ldf(w_norm + h * w_head_stride + d) * (gate_silu ? z * sigmoidf_(z) : sigmoidf_(z)));
@@ -535,7 +545,7 @@ __global__ void tanh_cols_kernel(const float* __restrict__ in, int ld, int col0,
 // ---------------------------------------------------------------------------------------------------------------------------
 // Products.  C[z][m, n] = sum_k A[z][m, k] * B[z][n, k]   with fp32 accumulation; A row-major (lda), B addressed by two strides
 // (sbn, sbk) so that a weight stored [K, N] is used without a transposed copy, z = batch (per-head products) via element offsets.
-// EPI 1: C = relu(C)^2.  EPI 2: C = xIELU(C) with the two raw parameters p, q at `epi` (in the weights' type).
+// EPI 1: C = relu(C)^2.  EPI 2: C = xIELU(C) with the two raw parameters p, q at `epi` (in the weights' type).  EPI 4: C = gelu(C), exact.
 // gemm_tiled_kernel: 64 x 64 x 16 shared-memory tiles, 256 threads, 4 x 4 outputs per thread, fp32 FMA (exact fp32 in the 32-bit mode).
 // ---------------------------------------------------------------------------------------------------------------------------
 template <typename TA, typename TB, typename TC, int EPI>
@@ -592,6 +602,7 @@ gemm_tiled_kernel(const TA* __restrict__ A, long lda, long a_batch, const TB* __
         float v = acc[i][j];
         if (EPI == 1) { v = fmaxf(v, 0.f); v *= v; }
         if (EPI == 2) v = xielu_f(v, ap, aq);
+        if (EPI == 4) v = gelu_erf_f(v);
         stf(C + (size_t)m * ldc + n, v);
       }
     }
@@ -681,6 +692,7 @@ gemv_rows_kernel(const TA* __restrict__ A, long lda, long a_batch, const TB* __r
       if (m < M && n0 + r < N) {
         if (EPI == 1) { v = fmaxf(v, 0.f); v *= v; }
         if (EPI == 2) v = xielu_f(v, softplusf_(ldf(epi)), 0.5f + softplusf_(ldf(epi + 1)));
+        if (EPI == 4) v = gelu_erf_f(v);
         stf(C + (size_t)m * ldc + n0 + r, v);
       }
     }

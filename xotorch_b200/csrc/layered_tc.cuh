@@ -6,7 +6,7 @@
 // (cp.async.bulk.tensor.3d, SWIZZLE_128B; coordinates {k, row, batch}), a single thread issues tcgen05.mma.cta_group::1.kind::f16
 // into a tensor-memory accumulator, four warps read it back with tcgen05.ld and store it (fp32 or bf16, optionally relu(.)^2).
 // Rows beyond M, columns beyond N and the tail of K come from the tensor map's zero fill, so no size has to be a multiple of the
-// tile.  EPI 1: relu(.)^2; EPI 2: xIELU; EPI 3: the columns come in groups of 16 = 8 gate values followed by their 8 up values, and
+// tile.  EPI 1: relu(.)^2; EPI 2: xIELU; EPI 4: exact gelu; EPI 3: the columns come in groups of 16 = 8 gate values followed by their 8 up values, and
 // C [*, N / 2] receives silu(gate) * up.  With `tile_batch` every row tile takes its B matrix from a list (grouped products: rows
 // sorted by expert).  The PTX wrappers are those of the shard engine's prefill GEMM (prefill_tc.cuh); what differs is the operand layout
 // (plain row-major weights, batched per-head products through the third coordinate), the epilogue and that EVERY wait is bounded:
@@ -153,6 +153,7 @@ ltc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           f[j] = __uint_as_float(v[j]);
           if (EPI == 1) { f[j] = fmaxf(f[j], 0.f); f[j] *= f[j]; }
           if (EPI == 2) f[j] = xielu_f(f[j], ap, aq);
+          if (EPI == 4) f[j] = gelu_erf_f(f[j]);
         }
         if (vec && n + 16 <= a.N) {
           float4* d4 = reinterpret_cast<float4*>(reinterpret_cast<float*>(crow) + n);

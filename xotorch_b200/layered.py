@@ -65,6 +65,25 @@ class LayerSpec:
   router_kind: int = _lib.LM_ROUTER_SOFTMAX_ALL
   router_bias: int = 0
   shared_ff: int = 0
+  rot_scale_factor: float = 0.0
+  rot_scale_low: float = 0.0
+  rot_scale_high: float = 0.0
+  rot_scale_original: float = 0.0
+  keep_first: int = 0
+  pool: int = 0
+  gate_cap: float = 0.0
+  out_norm_groups: int = 0
+  par_on: int = 0
+  par_mixer: int = 0
+  par_heads: int = 0
+  par_kv_heads: int = 0
+  par_dim: int = 0
+  par_vdim: int = 0
+  par_conv_taps: int = 0
+  par_out_norm_groups: int = 0
+  par_gate_cap: float = 0.0
+  mix_scale: float = 1.0
+  par_scale: float = 0.0
 
   def to_c(self) -> LmLayer:
     c = LmLayer()
@@ -229,8 +248,76 @@ def tunavik_globals(config: dict) -> dict:
               logit_scale=float(config.get("logit_scale", 1.0)), logit_softcap=float(config.get("logit_softcap") or 0.0))
 
 
+# ---- the Fubelorn family -----------------------------------------------------------------------------------------------------
+# config.json: {"architecture": "Fubelorn", "width", "vocab", "norm": {"eps"}, "residual_mult", "streams", "canon": {"taps"},
+#               "layers": [{"type", "mixer", "mlp"}]}
+# A layer is pre-norm with ONE-NUMBER norm weights: x += mult * sublayer(c(rms(x) * g)), c(h) = h + causal convolution of h over
+# time (canon.taps); the stream is kept in `streams` copies mixed by hyper-connections (l<i>.hc<q>.in / out / mix); embedding and
+# final norm are of the same kind.  Mixers:
+#   type "parallel"    left: attention without rotation, weightless RMS norm of every query / key head, sliding window mask.size that
+#                      keeps the first mask.keep_first tokens;  right: gated delta rule (heads, kv_heads, dim, vdim, conv)
+#   type "parallel_2"  left: rotary attention (rot {base, dims, scaling {factor, low, high, original}}, pairs (i, i + dims / 2)), sliding
+#                      window mask.size with pooled blocks of mask.pool tokens beyond it, one sigmoid gate per head;
+#                      right: matrix LSTM (heads, dim, vdim, gate_cap)
+#   type "mamba2"      state-space layer (heads, vdim, state, groups, norm_groups, conv)
+#   output of a two-mixer layer: left_scale * left + right_scale * right.        mlp.kind "dense": W_down gelu(W_up h) (mlp.ff)
+# Which options a left mixer has follows from its keys (rot, mask.keep_first, mask.pool) and from the layer type (query/key norm
+# for "parallel", head gate for "parallel_2").
+FUBELORN_LEFT = {"parallel": dict(qk_norm=_lib.LM_QKNORM_HEAD_PLAIN, out_gate=0), "parallel_2": dict(qk_norm=_lib.LM_QKNORM_NONE, out_gate=1)}
+
+
+def _fubelorn_attention(i: int, kind: str, m: dict) -> dict:
+  mask, rot = m.get("mask") or {}, m.get("rot") or None
+  out = dict(mixer=_lib.LM_MIX_ATTENTION, heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=int(m["dim"]), vdim=int(m["vdim"]),
+             scale=float(m["scale"]), window=int(mask.get("size", 0)), keep_first=int(mask.get("keep_first", 0)), pool=int(mask.get("pool", 0)),
+             **FUBELORN_LEFT[kind])
+  if rot:
+    out.update(rot_dims=int(rot["dims"]), rot_base=float(rot["base"]), rot_layout=_lib.LM_ROT_HALF)
+    sc = rot.get("scaling")
+    if sc:
+      out.update(rot_scale_factor=float(sc["factor"]), rot_scale_low=float(sc["low"]), rot_scale_high=float(sc["high"]), rot_scale_original=float(sc["original"]))
+  return out
+
+
+def _fubelorn_recurrent(i: int, kind: str, m: dict) -> dict:
+  """fields of a recurrent mixer under the names of a layer's FIRST mixer"""
+  if kind == "parallel":
+    return dict(mixer=_lib.LM_MIX_GATED_DELTA, heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                conv_taps=int(m["conv"]))
+  if kind == "parallel_2":
+    return dict(mixer=_lib.LM_MIX_MATRIX_LSTM, heads=int(m["heads"]), kv_heads=int(m["heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]), gate_cap=float(m["gate_cap"]))
+  return dict(mixer=_lib.LM_MIX_MAMBA2, heads=int(m["heads"]), kv_heads=int(m.get("groups", 1)), dim=int(m["state"]), vdim=int(m["vdim"]),
+              conv_taps=int(m["conv"]), out_norm_groups=int(m.get("norm_groups", 1)))
+
+
+def fubelorn_layers(config: dict, shapes: Dict[str, Tuple[int, ...]]) -> List[LayerSpec]:
+  out = []
+  for i, layer in enumerate(config["layers"]):
+    kind, m, mlp = layer["type"], layer["mixer"], layer.get("mlp")
+    if mlp is not None and mlp.get("kind", "dense") != "dense":
+      raise ValueError(f"layer {i}: feed-forward kind {mlp.get('kind')!r} is not implemented (dense)")
+    ff = dict(ff=int(mlp["ff"]) if mlp is not None else 0, ff_kind=_lib.LM_FF_GELU)
+    if kind in FUBELORN_LEFT:
+      right = _fubelorn_recurrent(i, kind, m["right"])
+      par = dict(par_on=1, par_mixer=right["mixer"], par_heads=right["heads"], par_kv_heads=right["kv_heads"], par_dim=right["dim"], par_vdim=right["vdim"],
+                 par_conv_taps=right.get("conv_taps", 0), par_out_norm_groups=right.get("out_norm_groups", 0), par_gate_cap=right.get("gate_cap", 0.0),
+                 mix_scale=float(m.get("left_scale", 1.0)), par_scale=float(m.get("right_scale", 1.0)))
+      out.append(LayerSpec(**_fubelorn_attention(i, kind, m["left"]), **par, **ff))
+    elif kind == "mamba2":
+      out.append(LayerSpec(**_fubelorn_recurrent(i, kind, m), **ff))
+    else:
+      raise ValueError(f"layer {i}: mixer type {kind!r} is not implemented")
+  return out
+
+
+def fubelorn_globals(config: dict) -> dict:
+  return dict(width=int(config["width"]), vocab=int(config["vocab"]), norm_groups=1, norm_eps=float(config["norm"]["eps"]),
+              block=_lib.LM_BLOCK_PRE_SCALAR, embed_norm=1, streams=int(config.get("streams", 0)),
+              canon_taps=int((config.get("canon") or {}).get("taps", 0)), residual_mult=float(config.get("residual_mult", 1.0)))
+
+
 LAYERED_FAMILIES = {"Zokuvik": (zokuvik_layers, zokuvik_globals), "Bufulorn": (bufulorn_layers, bufulorn_globals),
-                    "Tunavik": (tunavik_layers, tunavik_globals)}
+                    "Tunavik": (tunavik_layers, tunavik_globals), "Fubelorn": (fubelorn_layers, fubelorn_globals)}
 
 
 class LayeredShard:
@@ -288,6 +375,8 @@ class LayeredShard:
     cfg.pos_sinusoid, cfg.sinusoid_base = self.globals.get("pos_sinusoid", 0), self.globals.get("sinusoid_base", 0.0)
     cfg.embed_norm = self.globals.get("embed_norm", 0)
     cfg.logit_scale, cfg.logit_softcap = self.globals.get("logit_scale", 1.0), self.globals.get("logit_softcap", 0.0)
+    cfg.streams, cfg.canon_taps = self.globals.get("streams", 0), self.globals.get("canon_taps", 0)
+    cfg.residual_mult = self.globals.get("residual_mult", 0.0)
     cfg.dtype = _lib.LM_DTYPE_F32 if self.dtype == "float32" else _lib.LM_DTYPE_BF16
     arr = (LmLayer * len(specs))(*[s.to_c() for s in specs])
     h = C.c_void_p()
