@@ -19,8 +19,9 @@
  *                               in range; state = fp32 matrix + normaliser vector + maximum per head;
  *   XOTB200_LM_MIX_MAMBA2       state-space layer with one decay per head, input-dependent step size, short convolution on its
  *                               inputs, gate before a grouped RMS norm; state = fp32 matrix per head + the convolution's last inputs.
- * Any of the attention, gated-delta, matrix-LSTM and state-space mixers may run as the SECOND branch of a layer (par_on): both read
- * the same input (one product for all their projections) and the layer's mixer output is mix_scale * first + par_scale * second.
+ * A layer whose mixer is one of the last four kinds may carry a SECOND, recurrent mixer (par_on: gated delta rule, matrix LSTM or
+ * state-space): both read the same input (one product for all their projections) and the layer's mixer output is
+ * mix_scale * first + par_scale * second.
  * A layer wraps its sublayers in grouped RMS norms before and after them, or reads the stream itself and closes with a layer norm
  * or an RMS norm, or — pre-norm with one-number weights — reads `streams` copies of the residual stream through hyper-connections
  * and passes every sublayer input through a short causal convolution that is added to it (xotb200_lm_cfg.block); its feed-forward is dense (relu^2 or xIELU) or a mixture of experts (gated silu or relu^2
@@ -152,7 +153,10 @@ typedef struct xotb200_lm_layer {
    * keep_first > 0 (with a window): the first keep_first tokens of the request stay visible whatever the distance.
    * pool > 0 (with a window): every block of `pool` consecutive tokens (blocks counted from position 0) that lies wholly before a
    * row's window, b * pool + pool - 1 <= i - window, is seen as ONE key and value: the means of the block's cached keys and values. */
-  float rot_scale_factor, rot_scale_low, rot_scale_high, rot_scale_original;
+  float rot_scale_factor;
+  float rot_scale_low;
+  float rot_scale_high;
+  float rot_scale_original;
   int32_t keep_first;
   int32_t pool;
   /* -- MIX_MATRIX_LSTM: heads x (dim, vdim); q = W_q h / sqrt(dim), k, v; log gates i = cap tanh((W_i h + b) / cap),
@@ -165,8 +169,13 @@ typedef struct xotb200_lm_layer {
   int32_t out_norm_groups;
   /* -- a second mixer in the same layer (par_on = 1): tensors l<i>.mix.left.* (this mixer) and l<i>.mix.right.* (the second) ------ */
   int32_t par_on;
-  int32_t par_mixer;    /* XOTB200_LM_MIX_GATED_DELTA, MIX_MATRIX_LSTM, MIX_MAMBA2 or MIX_ATTENTION                              */
-  int32_t par_heads, par_kv_heads, par_dim, par_vdim, par_conv_taps, par_out_norm_groups;
+  int32_t par_mixer;    /* a recurrent kind: XOTB200_LM_MIX_GATED_DELTA, MIX_MATRIX_LSTM or MIX_MAMBA2                           */
+  int32_t par_heads;    /* the second mixer's sizes, under the names its kind gives them as a first mixer             */
+  int32_t par_kv_heads;
+  int32_t par_dim;
+  int32_t par_vdim;
+  int32_t par_conv_taps;
+  int32_t par_out_norm_groups;
   float par_gate_cap;
   float mix_scale;      /* the layer's mixer output = mix_scale * this mixer (0 = 1) + par_scale * the second                    */
   float par_scale;

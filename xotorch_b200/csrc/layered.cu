@@ -377,7 +377,6 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
       e->max_qfull = std::max(e->max_qfull, H * dk);
       e->max_oh = std::max(e->max_oh, H * dv);
       if (dk % 8 || dv % 8 || dk > 256 || dv > 128) e->gqa_flash_fits = false;
-      if (s.keep_first > 0 || s.pool > 0) e->gqa_flash_fits = false;   // the tensor-core prompt kernel walks one stretch of token keys
     } else if (s.mixer == XOTB200_LM_MIX_GATED_DELTA) {
       const int H = s.heads, G = s.kv_heads, dk = s.dim, dv = s.vdim, C = 2 * G * dk + H * dv;
       REQUIRE(G >= 1 && H % G == 0, "layer %d: %d value heads do not divide into %d query/key heads", li, H, G);
@@ -1456,8 +1455,6 @@ static int run_layers_pre_scalar(xotb200_lm* e, const StepPlan& sp, int n_want) 
     TRY((product<T, T, float, 0>(e, hw, D, 0, at<T>(e, e->head), D, 1, 0, e->logits, e->cfg.vocab, 0, n_want, e->cfg.vocab, D, 1)));
     finish_logits(e, n_want);
     CK(cudaGetLastError());
-  } else if (!e->last) {
-    TRY(open(nullptr, 0, e->h0));                      // a later shard continues from the summed stream
   }
   return 0;
 }
@@ -1702,7 +1699,8 @@ int xotb200_lm_load_tensor(xotb200_lm* e, const char* name, const void* bits, co
     return XOTB200_ESTRICT;
   }
   Dest& d = it->second;
-  const bool ok = (ndim == 2 && shape[0] == d.rows && shape[1] == d.cols) || (ndim == 1 && d.rows == 1 && shape[0] == d.cols);
+  const bool ok = (ndim == 2 && shape[0] == d.rows && shape[1] == d.cols) || (ndim == 1 && d.rows == 1 && shape[0] == d.cols) ||
+                  (ndim == 0 && d.rows == 1 && d.cols == 1);
   if (!ok) {
     set_err("tensor '%s': shape [%lld%s%lld] does not fit the model's [%d, %d]", name, (long long)shape[0], ndim > 1 ? ", " : "", ndim > 1 ? (long long)shape[1] : 0LL,
             d.rows, d.cols);

@@ -377,7 +377,8 @@ __global__ void gqa_combine_kernel(const float* __restrict__ part, const Item* _
 // into two buffers each (the next 64 keys are in flight while these are multiplied); Q, K fragments by ldmatrix, V transposed on
 // the way into registers by ldmatrix.trans; scores by mma.sync.m16n8k16 (bf16 operands, fp32 accumulators), then in fp32: scale,
 // soft cap, distance penalty, mask, running max and sum.  The softmax weights enter the value product as a bf16 PAIR (high part +
-// remainder, two MMAs) so that they keep 16 mantissa bits.
+// remainder, two MMAs) so that they keep 16 mantissa bits.  The keys are walked by their virtual index (kept first tokens or pooled
+// blocks in front of the token stretch, see gqa_extra_keys); distance terms go with layers that have no such keys.
 // ===========================================================================================================================
 // dist_table[a][d] = r1[a] * ln(1 + r2[a] * d) for d < n: the distance penalty of head a, made once per step and layer so that the
 // prompt kernel reads it instead of taking a logarithm per score
@@ -414,6 +415,8 @@ gqa_flash_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ pool, Pa
   const uint4 zero4 = make_uint4(0, 0, 0, 0);
   const int last = tl.pos0 + tl.n_rows - 1;
   const int first = gqa_first_key(tl.pos0, sc.window, sc.chunk);
+  const int extra = gqa_extra_keys(first, last, sc.window, sc.keep_first, sc.pool);   // keys in front of the token stretch (virtual index < extra)
+  const int vlast = extra + last - first;
   const int qc = DQP / 8;
   const size_t rowlen = (size_t)G * (dk + dv);
   const float* dtab = dist_table ? dist_table + (size_t)h * dist_n : nullptr;
@@ -421,22 +424,27 @@ gqa_flash_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ pool, Pa
   const bool dist_terms = dtab || rtab;
 
   // the page walk is done once per key (64 threads), then every thread copies 16-byte pieces from the rows it names
-  auto locate = [&](int j0, int bsel) {
-    if (threadIdx.x < 64) krow[bsel][threadIdx.x] = j0 + (int)threadIdx.x <= last ? pg.row(tl.slot, j0 + threadIdx.x) * rowlen : 0;
+  auto locate = [&](int v0, int bsel) {
+    if (threadIdx.x < 64) {
+      const int v = v0 + (int)threadIdx.x;
+      size_t r = 0;
+      if (v <= vlast) r = v >= extra ? pg.row(tl.slot, first + v - extra) : sc.pool > 0 ? sc.pool_rows + pg.row(tl.slot, v) : pg.row(tl.slot, v);
+      krow[bsel][threadIdx.x] = r * rowlen;
+    }
   };
-  auto issue = [&](int j0, int bsel) {
+  auto issue = [&](int j0, int bsel) {                   // j0: virtual index of the tile's first key
     bf16* kd = Ks + bsel * 64 * QS;
     for (int e = threadIdx.x; e < 64 * qc; e += 128) {
       const int r = e / qc, c = (e % qc) * 8, j = j0 + r;
       bf16* dst = kd + r * QS + c;
-      if (j > last || c >= dk) *reinterpret_cast<uint4*>(dst) = zero4;
+      if (j > vlast || c >= dk) *reinterpret_cast<uint4*>(dst) = zero4;
       else cp_async16_b(dst, pool + krow[bsel][r] + (size_t)g * dk + c);
     }
     bf16* vd = Vs + bsel * 64 * VS;
     for (int e = threadIdx.x; e < 64 * DVT; e += 128) {
       const int r = e / DVT, c = (e % DVT) * 8, j = j0 + r;
       bf16* dst = vd + r * VS + c;
-      if (j > last || c >= dv) *reinterpret_cast<uint4*>(dst) = zero4;
+      if (j > vlast || c >= dv) *reinterpret_cast<uint4*>(dst) = zero4;
       else cp_async16_b(dst, pool + krow[bsel][r] + (size_t)G * dk + (size_t)g * dv + c);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -455,14 +463,16 @@ gqa_flash_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ pool, Pa
   const int pos_lo = tl.pos0 + warp * 16 + gq, pos_hi = pos_lo + 8;
   // visible keys of this thread's two rows: [lo, pos] (the divisions of the block rule are done once, here)
   const int vis_lo[2] = {gqa_first_key(pos_lo, sc.window, sc.chunk), gqa_first_key(pos_hi, sc.window, sc.chunk)};
+  const int seen[2] = {sc.pool > 0 ? gqa_blocks_seen(pos_lo, sc.window, sc.pool) : 0, sc.pool > 0 ? gqa_blocks_seen(pos_hi, sc.window, sc.pool) : 0};
   const float inv_cap = sc.cap > 0.f ? 1.0f / sc.cap : 0.f;
-  const int ntile = (last - first) / 64 + 1;
-  locate(first, 0);
-  locate(first + 64, 1);
+  const int ntile = vlast / 64 + 1;
+  locate(0, 0);
+  locate(64, 1);
   __syncthreads();
-  issue(first, 0);
+  issue(0, 0);
   for (int it = 0; it < ntile; ++it) {
-    const int j0 = first + it * 64, bsel = it & 1;
+    const int v0 = it * 64, bsel = it & 1;
+    const int j0 = first + v0 - extra;                  // position of the tile's first key where it is a token (distance terms: extra == 0)
     if (dist_terms) {                                // distances pos0 - (j0 + 63) + index; negative ones belong to keys after the row (masked)
       const int d = tl.pos0 - j0 - 63 + (int)threadIdx.x;
       float b = 0.f;
@@ -471,13 +481,13 @@ gqa_flash_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ pool, Pa
       dpen[bsel][threadIdx.x] = b;
     }
     if (it + 1 < ntile) {
-      issue(j0 + 64, bsel ^ 1);
+      issue(v0 + 64, bsel ^ 1);
       asm volatile("cp.async.wait_group 1;" ::: "memory");
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
-    locate(j0 + 128, bsel);                          // krow[bsel] was last read by the issue of this tile; the next reader is two barriers away
+    locate(v0 + 128, bsel);                          // krow[bsel] was last read by the issue of this tile; the next reader is two barriers away
     const bf16* kt = Ks + bsel * 64 * QS;
     const bf16* vt = Vs + bsel * 64 * VS;
     float s[8][4];
@@ -499,8 +509,8 @@ gqa_flash_kernel(const bf16* __restrict__ q16, const bf16* __restrict__ pool, Pa
     for (int n = 0; n < 8; ++n)
 #pragma unroll
       for (int x = 0; x < 4; ++x) {
-        const int j = j0 + n * 8 + 2 * t + (x & 1), pos = (x < 2) ? pos_lo : pos_hi;
-        const bool vis = j <= last && j <= pos && j >= vis_lo[x >> 1];
+        const int v = v0 + n * 8 + 2 * t + (x & 1), j = first + v - extra, pos = (x < 2) ? pos_lo : pos_hi;
+        const bool vis = v < extra ? (sc.pool > 0 ? v < seen[x >> 1] : true) : (j <= last && j <= pos && (j >= vis_lo[x >> 1] || j < sc.keep_first));
         s[n][x] = vis ? gqa_adjust_fast(s[n][x], sc, inv_cap, dist_terms ? dpen[bsel] : nullptr, (pos - tl.pos0) - (j - j0) + 63) : -INFINITY;
         tmax[x >> 1] = fmaxf(tmax[x >> 1], s[n][x]);
       }
