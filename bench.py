@@ -490,9 +490,10 @@ def main():
   # the layered engine (models given as a list of layers: latent attention, delta rule) beside a Llama decoder of equal size;
   # an option of its own: the default workload above and its JSON line are untouched
   ap.add_argument("--layered", action="store_true", help="prefill / decode throughput of Zokuvik-shaped models next to a Llama of the same size")
-  ap.add_argument("--layered-family", default="zokuvik", choices=["zokuvik", "bufulorn", "tunavik"],
+  ap.add_argument("--layered-family", default="zokuvik", choices=["zokuvik", "bufulorn", "tunavik", "fubelorn"],
                   help="with --layered: the model family measured (bufulorn: next to a Zokuvik model of the same size; tunavik: next to a "
-                       "Bufulorn model of attention layers of the same size)")
+                       "Bufulorn model of attention layers of the same size; fubelorn: next to a Bufulorn model of gated-delta and attention "
+                       "layers with dense feed-forwards of the same size)")
   ap.add_argument("--layered-sizes", default="", help="comma list out of small,medium,large (default: all)")
   ap.add_argument("--layered-prompts", default="", help="prompt lengths (default 1024,4096)")
   args = ap.parse_args()

@@ -10,6 +10,11 @@ the same width and depth whose feed-forward size is chosen so that the weight by
 shared keys / values; relu^2 experts with a shared expert) beside the closest existing family on the same engine, a Bufulorn
 model of attention layers only with the same heads, layer pattern and (to a few per cent) weight bytes.
 
+`--layered-family fubelorn`: the same for Fubelorn-shaped models (two-mixer layers: rotary attention with pooled far blocks + matrix
+LSTM, windowed attention that keeps the first tokens + gated delta rule; state-space layers; hyper-connections over four copies of the
+stream, input convolutions, gelu feed-forwards) beside the closest existing family on the same engine, a Bufulorn model of gated-delta
+and attention layers with dense feed-forwards, of the same width and depth and (to a few per cent) weight bytes.
+
 Timing: every number is the device time of the step(s) (CUDA events on the engine's stream, `last_step_ms` / the ring's own
 timer), after warm-up; the weights of every size are larger than L2 from `medium` on, and each prompt step streams all of them.
 Roofline denominators come from MEASURED_PEAKS.json (fallback: the profiling recipe's numbers)."""
@@ -121,6 +126,50 @@ def bufulorn_attention_config(s: dict, b: dict, context: int):
   cfg = {"architecture": "Bufulorn", "width": s["width"], "vocab": s["vocab"], "max_positions": context, "norm": {"eps": 1e-5}, "layers": layers}
   idle = len(layers) * (EXPERTS - TOP) * 3 * fb * s["width"] * 2
   return cfg, idle
+
+
+# Fubelorn shapes at the same widths, per repeat [rotary pooled attention + matrix LSTM, kept-first attention + gated delta rule,
+# state-space layer], every layer with a dense gelu feed-forward; attention heads as the Bufulorn attention layers; the state-space layer
+# has 2 * width channels in heads of 64 with 128 states; four copies of the stream, four-tap input convolutions, window 1024 with
+# blocks of 64 pooled beyond it resp. the first 4 tokens kept
+FUBELORN = {
+  "small": dict(lheads=4, ldim=64, lvdim=64, sheads=32, svdim=64, state=128),
+  "medium": dict(lheads=8, ldim=64, lvdim=128, sheads=64, svdim=64, state=128),
+  "large": dict(lheads=16, ldim=128, lvdim=128, sheads=128, svdim=64, state=128),
+}
+FUB_STREAMS, FUB_POOL, FUB_KEEP = 4, 64, 4
+
+
+def fubelorn_config(s: dict, b: dict, f: dict):
+  def left(kind):
+    m = {"heads": b["heads"], "kv_heads": b["kv_heads"], "dim": b["dim"], "vdim": b["vdim"], "scale": float(b["dim"] ** -0.5)}
+    if kind == "parallel":
+      m["mask"] = {"size": WINDOW, "keep_first": FUB_KEEP}
+    else:
+      m["mask"] = {"size": WINDOW, "pool": FUB_POOL}
+      m["rot"] = {"base": 500000.0, "dims": b["dim"], "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    return m
+  dense = {"kind": "dense", "ff": s["ff"]}
+  layers = []
+  for _ in range(s["repeats"]):
+    layers += [{"type": "parallel_2", "mixer": {"left": left("parallel_2"), "right": {"heads": f["lheads"], "dim": f["ldim"], "vdim": f["lvdim"], "gate_cap": 15.0},
+                                                 "left_scale": 0.7, "right_scale": 0.7}, "mlp": dense},
+               {"type": "parallel", "mixer": {"left": left("parallel"), "right": {"heads": b["dheads"], "kv_heads": b["dkv"], "dim": b["ddim"], "vdim": b["dvdim"], "conv": TAPS},
+                                               "left_scale": 0.7, "right_scale": 0.7}, "mlp": dense},
+               {"type": "mamba2", "mixer": {"heads": f["sheads"], "vdim": f["svdim"], "state": f["state"], "groups": 1, "norm_groups": 1, "conv": TAPS}, "mlp": dense}]
+  return {"architecture": "Fubelorn", "width": s["width"], "vocab": s["vocab"], "norm": {"eps": 1e-6}, "residual_mult": 0.5, "streams": FUB_STREAMS,
+          "canon": {"taps": TAPS}, "layers": layers}
+
+
+def bufulorn_dense_config(s: dict, b: dict, context: int, ff: int):
+  """Bufulorn layers with dense feed-forwards only: per repeat [gated delta rule, attention, attention], causal within blocks of 1024"""
+  dense = {"kind": "dense", "ff": ff}
+  att = {"type": "attention", "mixer": {"heads": b["heads"], "kv_heads": b["kv_heads"], "dim": b["dim"], "vdim": b["vdim"], "scale": float(b["dim"] ** -0.5), "softcap": 30.0,
+                                        "mask": {"size": WINDOW}}, "mlp": dense}
+  layers = []
+  for _ in range(s["repeats"]):
+    layers += [{"type": "delta", "mixer": {"heads": b["dheads"], "kv_heads": b["dkv"], "dim": b["ddim"], "vdim": b["dvdim"], "conv": TAPS}, "mlp": dense}, att, att]
+  return {"architecture": "Bufulorn", "width": s["width"], "vocab": s["vocab"], "max_positions": context, "norm": {"eps": 1e-5}, "layers": layers}
 
 
 def peaks():
@@ -285,6 +334,33 @@ def run_tunavik(args, sizes, prompts, hbm, tf, src) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_fubelorn(args, sizes, prompts, hbm, tf, src) -> None:
+  from .layered import LayeredShard
+  for name in sizes:
+    s, b, f = SIZES[name], BUFULORN[name], FUBELORN[name]
+    warm = max(3, args.warmup)
+    context = max(max(prompts), 1024 + 9 * (args.steps * 8 + warm)) + 64
+    cfg = fubelorn_config(s, b, f)
+    fu = layered_numbers(s, prompts, decode_ctx=1024, decode_batches=[1, 8], steps=args.steps, warmup=warm, cfg=cfg)
+    def nbytes(ff):
+      eng = LayeredShard(bufulorn_dense_config(s, b, context, ff), 0, "bfloat16")
+      eng.set_shard(0, 3 * s["repeats"] - 1, {})
+      n = eng.weight_bytes()
+      eng.close()
+      return n
+    b0, b1 = nbytes(1024), nbytes(2048)
+    ff = int(max(256, 1024 + (fu["weight_bytes"] - b0) / ((b1 - b0) / 1024)) // 64 * 64)
+    bu = layered_numbers(s, prompts, decode_ctx=1024, decode_batches=[1, 8], steps=args.steps, warmup=warm, cfg=bufulorn_dense_config(s, b, context, ff))
+    line = {"bench": "layered", "family": "fubelorn", "size": name, "dtype": "bf16", "data": "synthetic", "shape": dict(s, **b, **f), "fubelorn": fu,
+            "bufulorn_same_size": bu, "bufulorn_ff": ff, "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src},
+            "frac_of_peak": {
+              "fubelorn_decode1_hbm": round(fu["decode"]["1"]["gbs_weights_device"] / hbm, 3),
+              "bufulorn_decode1_hbm": round(bu["decode"]["1"]["gbs_weights_device"] / hbm, 3),
+              **{f"fubelorn_prefill{n}_tensor": round(fu["prefill"][str(n)]["tflops_weights"] / tf, 3) for n in prompts},
+              **{f"bufulorn_prefill{n}_tensor": round(bu["prefill"][str(n)]["tflops_weights"] / tf, 3) for n in prompts}}}
+    print(json.dumps(line), flush=True)
+
+
 def run(args) -> None:
   hbm, tf, src = peaks()
   sizes = [x for x in (args.layered_sizes or "small,medium,large").split(",") if x]
@@ -293,6 +369,8 @@ def run(args) -> None:
     return run_bufulorn(args, sizes, prompts, hbm, tf, src)
   if getattr(args, "layered_family", "") == "tunavik":
     return run_tunavik(args, sizes, prompts, hbm, tf, src)
+  if getattr(args, "layered_family", "") == "fubelorn":
+    return run_fubelorn(args, sizes, prompts, hbm, tf, src)
   for name in sizes:
     s = SIZES[name]
     z = layered_numbers(s, prompts, decode_ctx=1024, decode_batches=[1, 8], steps=args.steps, warmup=max(3, args.warmup))

@@ -101,7 +101,7 @@ struct LmLayer {
   // feed-forward forms: xIELU parameters; mixture of experts: router [E, D], experts' [E][2 F, D] (gate rows, up rows) and [E][D, F]
   size_t act_p = 0, router = 0, router_b = 0, w_gu = 0, w_edown = 0;   // a shared expert's matrices are `up` / `down`
   // matrix LSTM: gate biases, float offset of the running maxima in a slot's block; state-space layer: filter bias, skip weights
-  size_t i_b = 0, f_b = 0, conv_b = 0, d_skip = 0, m_off = 0;
+  size_t i_b = 0, f_b = 0, conv_b = 0, d_skip = 0, m_off = 0, n_off = 0;
   int c_i = 0, c_f = 0, c_z = 0, c_dt = 0;
   int ld_in = 0;                                       // leading dimension of the projection output this mixer reads (all mixers of the layer)
   std::vector<LmLayer> par;                            // the layer's second mixer (0 or 1 entries): reads the same input, output added
@@ -157,9 +157,9 @@ struct xotb200_lm {
   float* dist_tab = nullptr;                           // prompt attention: distance penalties per head and distance, remade per layer
   size_t dist_cap = 0;
   int max_conv = 0, max_top = 0, max_eff = 0, max_experts = 0;
-  float *y2 = nullptr, *h0 = nullptr, *gdec = nullptr, *ginw = nullptr, *gfloor = nullptr, *vaug = nullptr;   // second mixer's output, normed input
-                                                       // before its convolution, matrix-LSTM gates per (row, head), values with the normaliser column
-  int max_heads_rec = 0, max_vaug = 0;
+  float *y2 = nullptr, *h0 = nullptr, *gdec = nullptr, *ginw = nullptr, *gfloor = nullptr, *gnq = nullptr;   // second mixer's output, normed input
+                                                       // before its convolution, matrix-LSTM decay / input weight / floor / n . q per (row, head)
+  int max_heads_rec = 0;
   bool pre_scalar = false;
   size_t final_norm_b = 0, pos_table = 0;
   void *h = nullptr, *cqn = nullptr, *qn = nullptr, *olat = nullptr, *oh = nullptr, *act = nullptr, *th = nullptr, *hw = nullptr;
@@ -410,7 +410,7 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
       e->max_conv = std::max(e->max_conv, C);
     } else if (s.mixer == XOTB200_LM_MIX_MATRIX_LSTM) {
       const int H = s.heads, dk = s.dim, dv = s.vdim;
-      REQUIRE(dk <= 256 && dv >= 1 && dv + 1 <= 256, "layer %d: matrix-LSTM head sizes %d / %d above 256 / 255", li, dk, dv);
+      REQUIRE(dk <= 256 && dv >= 1 && dv <= 256, "layer %d: matrix-LSTM head sizes %d / %d above 256", li, dk, dv);
       REQUIRE(s.gate_cap > 0.f, "layer %d: the gates' cap must be positive", li);
       // projection columns: q | k | v | output gate | input-gate logits | forget-gate logits
       L.c_r = cb; L.c_k = cb + H * dk; L.c_v = cb + 2 * H * dk; L.c_g = L.c_v + H * dv; L.c_i = L.c_g + H * dv; L.c_f = L.c_i + H;
@@ -426,14 +426,15 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
       L.f_b = take(H); dest(mp + "f.b", L.f_b, 1, H, 0);
       L.onorm = take((size_t)H * dv); dest(mp + "norm", L.onorm, 1, H * dv, 0);
       L.wo = take((size_t)D * H * dv); dest(mp + "o", L.wo, D, H * dv, 0);
-      L.state_off = e->state_floats;                       // per head [dk, dv + 1]: the last column is the normaliser
-      e->state_floats += (size_t)H * dk * (dv + 1);
+      L.state_off = e->state_floats;                       // per head the matrix [dk, dv], then the normalisers [H, dk], then the maxima [H]
+      e->state_floats += (size_t)H * dk * dv;
+      L.n_off = e->state_floats;
+      e->state_floats += (size_t)H * dk;
       L.m_off = e->state_floats;
       e->state_floats += (size_t)H;
-      e->max_hd = std::max(e->max_hd, H * std::max(dk, dv + 1));
+      e->max_hd = std::max(e->max_hd, H * std::max(dk, dv));
       e->max_oh = std::max(e->max_oh, H * dv);
       e->max_heads_rec = std::max(e->max_heads_rec, H);
-      e->max_vaug = std::max(e->max_vaug, H * (dv + 1));
     } else if (s.mixer == XOTB200_LM_MIX_MAMBA2) {
       const int H = s.heads, G = s.kv_heads, N = s.dim, dv = s.vdim, inner = H * dv, C = inner + 2 * G * N;
       REQUIRE(G >= 1 && H % G == 0, "layer %d: %d heads do not divide into %d groups", li, H, G);
@@ -728,7 +729,7 @@ static int ensure_scratch(xotb200_lm* e, int M, int n_want) {
       TRY(regrow(e->gdec, m * e->max_heads_rec * 4));
       TRY(regrow(e->ginw, m * e->max_heads_rec * 4));
       TRY(regrow(e->gfloor, m * e->max_heads_rec * 4));
-      TRY(regrow(e->vaug, m * e->max_vaug * 4));
+      TRY(regrow(e->gnq, m * e->max_heads_rec * 4));
     }
     TRY(regrow(e->proj, m * e->max_in * 4));
     TRY(regrow(e->qraw, m * e->max_q * 4));
@@ -985,7 +986,7 @@ static int delta_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
   CK(cudaGetLastError());
   e->launches++;
   TRY(run_delta(e, L, sp, DeltaSrc{e->proj, L.n_in, L.c_k}, DeltaSrc{e->proj, L.n_in, L.c_r}, DeltaSrc{e->proj, L.n_in, L.c_v}, s.dim, s.vdim, true));
-  head_norm_gate_kernel<T><<<cdiv((long)M * s.heads, 8), 256, 0, e->stream>>>(e->oraw, s.vdim, nullptr, at<T>(e, L.onorm), s.vdim, e->proj, L.n_in, L.c_g, 0,
+  head_norm_gate_kernel<T><<<cdiv((long)M * s.heads, 8), 256, 0, e->stream>>>(e->oraw, nullptr, nullptr, at<T>(e, L.onorm), s.vdim, e->proj, L.n_in, L.c_g, 0,
                                                                                static_cast<T*>(e->oh), s.heads, s.vdim, e->cfg.norm_eps, M);
   CK(cudaGetLastError());
   e->launches++;
@@ -1040,9 +1041,10 @@ static int gqa_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp, float* yout)
   CK(cudaGetLastError());
   e->launches++;
   const size_t pool_rows = (size_t)e->n_pages * e->page_size;
-  if (s.pool > 0 && (sp.max_rows + s.pool - 1) / s.pool + 1 > 0) {
+  if (s.pool > 0) {
     // blocks whose last token this step appended get their pooled row (after the append, before any reader)
-    gqa_pool_blocks_kernel<T><<<dim3(sp.n_seq, sp.max_rows / s.pool + 1), 128, 0, e->stream>>>(pool, pg, pool_rows, sp.seqs, s.pool, G * (dk + dv));
+    gqa_pool_blocks_kernel<T><<<dim3(sp.n_seq, sp.max_rows / s.pool + 1, cdiv(G * (dk + dv), 128)), 128, 0, e->stream>>>(pool, pg, pool_rows, sp.seqs, s.pool,
+                                                                                                                       G * (dk + dv));
     CK(cudaGetLastError());
     e->launches++;
   }
@@ -1115,7 +1117,7 @@ static int gqa_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp, float* yout)
 }
 
 // short causal convolution of C projection columns starting at col0 (filter inputs of earlier steps from the slot's state, which
-// then moves on) -> e->cvb [M, C]
+// the same launch then moves on) -> e->cvb [M, C]
 template <typename T>
 static int filter_channels(xotb200_lm* e, LmLayer& L, const StepPlan& sp, int col0, int C, const T* bias) {
   const xotb200_lm_layer& s = L.s;
@@ -1125,11 +1127,6 @@ static int filter_channels(xotb200_lm* e, LmLayer& L, const StepPlan& sp, int co
                                                                                           sp.seqs, cstate, e->state_floats, e->cvb, C);
   CK(cudaGetLastError());
   e->launches++;
-  if (s.conv_taps > 1) {
-    conv_state_update_kernel<<<dim3(sp.n_seq, cdiv(C, 256)), 256, 0, e->stream>>>(e->proj, L.ld_in, col0, C, s.conv_taps, sp.seqs, cstate, e->state_floats);
-    CK(cudaGetLastError());
-    e->launches++;
-  }
   return 0;
 }
 
@@ -1143,7 +1140,7 @@ static int gated_delta_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp, floa
   CK(cudaGetLastError());
   e->launches++;
   TRY(run_delta(e, L, sp, DeltaSrc{e->dkk, H * dk, 0}, DeltaSrc{e->drr, H * dk, 0}, DeltaSrc{e->cvb, C, 2 * G * dk}, dk, dv, true));
-  head_norm_gate_kernel<T><<<cdiv((long)M * H, 8), 256, 0, e->stream>>>(e->oraw, dv, nullptr, at<T>(e, L.onorm), 0, e->proj, L.ld_in, L.c_g, 1, static_cast<T*>(e->oh),
+  head_norm_gate_kernel<T><<<cdiv((long)M * H, 8), 256, 0, e->stream>>>(e->oraw, nullptr, nullptr, at<T>(e, L.onorm), 0, e->proj, L.ld_in, L.c_g, 1, static_cast<T*>(e->oh),
                                                                        H, dv, e->cfg.norm_eps, M);
   CK(cudaGetLastError());
   e->launches++;
@@ -1151,8 +1148,8 @@ static int gated_delta_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp, floa
   return 0;
 }
 
-// matrix LSTM: gates (a scan per request and head), vectors, the shared recurrence kernel on [dk, dv + 1] states, normaliser +
-// head norm + sigmoid gate, output product
+// matrix LSTM: gates (a scan per request and head), vectors, the normaliser's own small recurrence, the shared recurrence kernel on
+// the [dk, dv] states, normaliser + head norm + sigmoid gate, output product
 template <typename T>
 static int matrix_lstm_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp, float* yout) {
   const xotb200_lm_layer& s = L.s;
@@ -1160,11 +1157,14 @@ static int matrix_lstm_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp, floa
   mlstm_gates_kernel<T><<<cdiv((long)sp.n_seq * H, 4), 128, 0, e->stream>>>(e->proj, L.ld_in, L.c_i, L.c_f, at<T>(e, L.i_b), at<T>(e, L.f_b), s.gate_cap, sp.seqs, sp.n_seq, H,
                                                                           e->state + L.m_off, e->state_floats, e->gdec, e->ginw, e->gfloor);
   CK(cudaGetLastError());
-  mlstm_expand_kernel<<<cdiv((long)M * H, 8), 256, 0, e->stream>>>(e->proj, L.ld_in, L.c_r, L.c_k, L.c_v, e->gdec, e->ginw, e->wlog, e->dkk, e->drr, e->vaug, H, dk, dv, M);
+  mlstm_expand_kernel<<<cdiv((long)M * H, 8), 256, 0, e->stream>>>(e->proj, L.ld_in, L.c_r, L.c_k, e->gdec, e->ginw, e->wlog, e->dkk, e->drr, H, dk, M);
   CK(cudaGetLastError());
-  e->launches += 2;
-  TRY(run_delta(e, L, sp, DeltaSrc{e->dkk, H * dk, 0}, DeltaSrc{e->drr, H * dk, 0}, DeltaSrc{e->vaug, H * (dv + 1), 0}, dk, dv + 1, false));
-  head_norm_gate_kernel<T><<<cdiv((long)M * H, 8), 256, 0, e->stream>>>(e->oraw, dv + 1, e->gfloor, at<T>(e, L.onorm), dv, e->proj, L.ld_in, L.c_g, 0,
+  mlstm_normaliser_kernel<<<sp.n_seq * H, 32 * std::max(1, std::min(16, sp.max_rows / 16)), 0, e->stream>>>(e->dkk, e->drr, e->gdec, sp.seqs, H, dk, e->state + L.n_off,
+                                                                                                        e->state_floats, e->gnq);
+  CK(cudaGetLastError());
+  e->launches += 3;
+  TRY(run_delta(e, L, sp, DeltaSrc{e->dkk, H * dk, 0}, DeltaSrc{e->drr, H * dk, 0}, DeltaSrc{e->proj, L.ld_in, L.c_v}, dk, dv, false));
+  head_norm_gate_kernel<T><<<cdiv((long)M * H, 8), 256, 0, e->stream>>>(e->oraw, e->gnq, e->gfloor, at<T>(e, L.onorm), dv, e->proj, L.ld_in, L.c_g, 0,
                                                                        static_cast<T*>(e->oh), H, dv, e->cfg.norm_eps, M);
   CK(cudaGetLastError());
   e->launches++;
@@ -1184,8 +1184,13 @@ static int mamba2_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp, float* yo
   CK(cudaGetLastError());
   e->launches++;
   TRY(run_delta(e, L, sp, DeltaSrc{e->dkk, H * N, 0}, DeltaSrc{e->drr, H * N, 0}, DeltaSrc{e->cvb, C, 0}, N, dv, false));
-  mamba2_out_kernel<T><<<cdiv((long)M * s.out_norm_groups, 8), 256, 0, e->stream>>>(e->oraw, e->cvb, C, e->proj, L.ld_in, L.c_z, at<T>(e, L.d_skip), at<T>(e, L.onorm), H, dv,
-                                                                                   s.out_norm_groups, e->cfg.norm_eps, static_cast<T*>(e->oh), M);
+  {
+    const int part = inner / s.out_norm_groups;
+    auto ok = mamba2_out_kernel<T>;
+    TRY(opt_in_smem(ok, (size_t)part * 4));
+    ok<<<M * s.out_norm_groups, std::min(1024, std::max(32, cdiv(part, 4 * 32) * 32)), (size_t)part * 4, e->stream>>>(
+        e->oraw, e->cvb, C, e->proj, L.ld_in, L.c_z, at<T>(e, L.d_skip), at<T>(e, L.onorm), H, dv, s.out_norm_groups, e->cfg.norm_eps, static_cast<T*>(e->oh));
+  }
   CK(cudaGetLastError());
   e->launches++;
   TRY((product<T, T, float, 0>(e, static_cast<T*>(e->oh), (long)inner, 0, at<T>(e, L.wo), (long)inner, 1, 0, yout, D, 0, M, D, inner, 1)));
@@ -1385,15 +1390,17 @@ static int run_layers_post(xotb200_lm* e, const StepPlan& sp, int n_want) {
 
 // Pre-norm layers with one-number norm weights: x += mult * sublayer(c(rms(x) * g)), the stream kept in `streams` copies mixed by
 // hyper-connections, c(h) = h + causal convolution of h.  hc_open_kernel closes the pending sublayer and opens the next in one
-// pass; the convolution (whose inputs of earlier steps are part of a slot's state) follows as a launch of its own.
+// pass; the convolution (whose inputs of earlier steps are part of a slot's state, moved on by the same launch) follows.
 template <typename T>
 static int run_layers_pre_scalar(xotb200_lm* e, const StepPlan& sp, int n_want) {
   const int D = e->cfg.width, M = sp.M, S = std::max(1, e->cfg.streams), CT = e->cfg.canon_taps;
   const bool hc = e->cfg.streams > 0;
   const float eps = e->cfg.norm_eps, mult = e->cfg.residual_mult != 0.f ? e->cfg.residual_mult : 1.0f;
   T* h = static_cast<T*>(e->h);
-  const int nt = std::min(1024, std::max(128, cdiv(D, 4 * 32) * 32));
-  auto okern = hc_open_kernel<T>;
+  const int nt = std::min(512, std::max(64, cdiv(D, 4 * 32) * 32));    // the row kernels keep all copies of an entry in registers
+  // copies held per entry: the smallest of 1, 2, 4, 8 that holds them; 16-byte loads when the rows allow
+  auto okern = D % 4 == 0 ? (S <= 1 ? hc_open_kernel<T, 1, 4> : S <= 2 ? hc_open_kernel<T, 2, 4> : S <= 4 ? hc_open_kernel<T, 4, 4> : hc_open_kernel<T, 8, 4>)
+                          : (S <= 1 ? hc_open_kernel<T, 1, 1> : S <= 2 ? hc_open_kernel<T, 2, 1> : S <= 4 ? hc_open_kernel<T, 4, 1> : hc_open_kernel<T, 8, 1>);
   TRY(opt_in_smem(okern, (size_t)D * 4));
   // the pending sublayer: its output(s), their scales and its hyper-connection coefficients
   struct Pending { const float *y = nullptr, *y2 = nullptr; float ya = 1.f, yb = 0.f; const T *mix = nullptr, *out = nullptr; } pend;
@@ -1415,11 +1422,6 @@ static int run_layers_pre_scalar(xotb200_lm* e, const StepPlan& sp, int n_want) 
                                                                                           e->state_floats, h, D);
       CK(cudaGetLastError());
       e->launches++;
-      if (CT > 1) {
-        conv_state_update_kernel<<<dim3(sp.n_seq, cdiv(D, 256)), 256, 0, e->stream>>>(e->h0, D, 0, D, CT, sp.seqs, cstate, e->state_floats);
-        CK(cudaGetLastError());
-        e->launches++;
-      }
     }
     return 0;
   };
@@ -1674,7 +1676,7 @@ int xotb200_lm_destroy(xotb200_lm* e) {
     if (L.rel_bucket) cudaFree(L.rel_bucket);
     if (L.rel_tab) cudaFree(L.rel_tab);
   }
-  void* ptrs[] = {e->y2, e->h0, e->gdec, e->ginw, e->gfloor, e->vaug, e->pos_freqs, e->dist_tab, e->moe_xg, e->moe_yg, e->moe_plan, e->dkk, e->drr, e->cvb, e->moe_ids, e->moe_wts, e->mact, e->du, e->dau, e->part, e->q16, e->cbuf, e->knx, e->vxx, e->blob, e->d_stage, e->x, e->y, e->proj, e->qraw, e->qfull, e->wlog, e->oraw, e->logits, e->h, e->cqn, e->qn, e->olat, e->oh, e->act,
+  void* ptrs[] = {e->y2, e->h0, e->gdec, e->ginw, e->gfloor, e->gnq, e->pos_freqs, e->dist_tab, e->moe_xg, e->moe_yg, e->moe_plan, e->dkk, e->drr, e->cvb, e->moe_ids, e->moe_wts, e->mact, e->du, e->dau, e->part, e->q16, e->cbuf, e->knx, e->vxx, e->blob, e->d_stage, e->x, e->y, e->proj, e->qraw, e->qfull, e->wlog, e->oraw, e->logits, e->h, e->cqn, e->qn, e->olat, e->oh, e->act,
                   e->th, e->hw, e->d_argmax, e->trace_buf};
   for (void* p : ptrs)
     if (p) cudaFree(p);

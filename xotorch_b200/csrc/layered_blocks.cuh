@@ -143,19 +143,22 @@ __global__ void residual_rmsnorm_kernel(float* __restrict__ x, const float* __re
 // act: 0 none, 1 silu.  in(p, c) is the input of the request's token at position p: a row of this step when p >= the step's first
 // position of the request, else one of the last taps-1 inputs of earlier steps, kept per slot in `state` ([taps - 1][C] fp32, zero
 // at the start of a request, so positions before 0 read as zero).  TO = float or the storage type (the operand of a product).
-// grid (requests, ceil(C / 256), row lanes).  conv_state_update_kernel then moves the window: it must run after every reader of
-// the old state.
+// grid (requests, ceil(C / 256), row stretches): stretch z takes rows [z * per, (z + 1) * per) with per >= taps - 1, so only stretch 0
+// reads the state — and the thread that read channel c's state moves that channel's window on afterwards (the last taps - 1 inputs
+// of the request so far), in the same launch.
 // ---------------------------------------------------------------------------------------------------------------------------
 template <typename T, typename TO>
 __global__ void short_conv_kernel(const float* __restrict__ proj, int ld, int col0, int C, const T* __restrict__ w, const T* __restrict__ bias, int taps,
-                                  int act, int residual, const Item* __restrict__ seqs, const float* __restrict__ state, size_t state_slot_stride,
+                                  int act, int residual, const Item* __restrict__ seqs, float* __restrict__ state, size_t state_slot_stride,
                                   TO* __restrict__ out, int ld_out) {
   const Item sq = seqs[blockIdx.x];
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= C) return;
-  const float* st = state + (size_t)sq.slot * state_slot_stride;
+  float* st = state + (size_t)sq.slot * state_slot_stride;
   const float b = bias ? ldf(bias + c) : 0.f;
-  for (int t = blockIdx.z; t < sq.n_rows; t += gridDim.z) {
+  const int per = max((sq.n_rows + (int)gridDim.z - 1) / (int)gridDim.z, taps - 1);
+  const int t_begin = blockIdx.z * per, t_end = min(sq.n_rows, t_begin + per);
+  for (int t = t_begin; t < t_end; ++t) {
     float acc = b;
     for (int i = 0; i < taps; ++i) {
       const int back = taps - 1 - i, src = t - back;           // row of this step, or (negative) before it
@@ -166,17 +169,11 @@ __global__ void short_conv_kernel(const float* __restrict__ proj, int ld, int co
     if (residual) acc += proj[(size_t)(sq.row0 + t) * ld + col0 + c];
     stf(out + (size_t)(sq.row0 + t) * ld_out + c, acc);
   }
-}
-__global__ void conv_state_update_kernel(const float* __restrict__ proj, int ld, int col0, int C, int taps, const Item* __restrict__ seqs,
-                                         float* __restrict__ state, size_t state_slot_stride) {
-  const Item sq = seqs[blockIdx.x];
-  const int c = blockIdx.y * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  float* st = state + (size_t)sq.slot * state_slot_stride;
-  for (int i = 0; i < taps - 1; ++i) {                         // increasing i: entry i + n_rows is still the old one when it is read
-    const int src = sq.n_rows + i - (taps - 1);
-    st[(size_t)i * C + c] = src >= 0 ? proj[(size_t)(sq.row0 + src) * ld + col0 + c] : st[(size_t)(i + sq.n_rows) * C + c];
-  }
+  if (blockIdx.z == 0)
+    for (int i = 0; i < taps - 1; ++i) {                       // increasing i: entry i + n_rows is still the old one when it is read
+      const int src = sq.n_rows + i - (taps - 1);
+      st[(size_t)i * C + c] = src >= 0 ? proj[(size_t)(sq.row0 + src) * ld + col0 + c] : st[(size_t)(i + sq.n_rows) * C + c];
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------------
@@ -634,11 +631,11 @@ __global__ void embed_streams_kernel(const T* __restrict__ embed, const int* __r
   }
 }
 
-template <typename T>
+template <typename T, int SM, int VEC>   // SM: copies held per entry (>= S); VEC: entries per thread and pass (4: 16-byte loads, D % 4 == 0)
 __global__ void hc_open_kernel(float* __restrict__ X, int S, const float* __restrict__ y, const float* __restrict__ y2, float ya, float yb, float mult,
                                const T* __restrict__ mix, const T* __restrict__ outc, const T* __restrict__ inc, const T* __restrict__ g, float eps,
                                const int* __restrict__ src_rows, float* __restrict__ out_f32, T* __restrict__ out_t, int D) {
-  extern __shared__ float hc_row[];
+  extern __shared__ __align__(16) float hc_row[];
   __shared__ float red[32];
   __shared__ float c_mix[HC_MAX_STREAMS * HC_MAX_STREAMS], c_out[HC_MAX_STREAMS], c_in[HC_MAX_STREAMS];
   const int m = blockIdx.x;
@@ -651,44 +648,70 @@ __global__ void hc_open_kernel(float* __restrict__ X, int S, const float* __rest
   __syncthreads();
   float* xr = X + xm * S * D;
   float ss = 0.f;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float xs[HC_MAX_STREAMS];
+  for (int d = threadIdx.x * VEC; d < D; d += blockDim.x * VEC) {
+    float xs[SM][VEC];
 #pragma unroll
-    for (int s = 0; s < HC_MAX_STREAMS; ++s) xs[s] = s < S ? xr[(size_t)s * D + d] : 0.f;
-    if (y) {
-      const float yv = ya * y[xm * D + d] + (y2 ? yb * y2[xm * D + d] : 0.f);
-      float nx[HC_MAX_STREAMS];
-#pragma unroll
-      for (int t = 0; t < HC_MAX_STREAMS; ++t) {
-        float a = 0.f;
-        if (t < S) {
-#pragma unroll
-          for (int s = 0; s < HC_MAX_STREAMS; ++s)
-            if (s < S) a = fmaf(c_mix[s * S + t], xs[s], a);
-          a = fmaf(c_out[t], yv, a);
+    for (int s = 0; s < SM; ++s) {
+      if (s < S) {
+        if constexpr (VEC == 4) {
+          const float4 v = *reinterpret_cast<const float4*>(xr + (size_t)s * D + d);
+          xs[s][0] = v.x; xs[s][1] = v.y; xs[s][2] = v.z; xs[s][3] = v.w;
+        } else {
+          xs[s][0] = xr[(size_t)s * D + d];
         }
-        nx[t] = a;
-      }
+      } else {
 #pragma unroll
-      for (int t = 0; t < HC_MAX_STREAMS; ++t) {
-        xs[t] = nx[t];
-        if (t < S && !src_rows) xr[(size_t)t * D + d] = nx[t];
+        for (int v = 0; v < VEC; ++v) xs[s][v] = 0.f;
       }
     }
-    float u = 0.f;
+    if (y) {
+      float yv[VEC];
 #pragma unroll
-    for (int s = 0; s < HC_MAX_STREAMS; ++s)
-      if (s < S) u = fmaf(c_in[s], xs[s], u);
-    hc_row[d] = u;
-    ss = fmaf(u, u, ss);
+      for (int v = 0; v < VEC; ++v) yv[v] = ya * y[xm * D + d + v] + (y2 ? yb * y2[xm * D + d + v] : 0.f);
+      float nx[SM][VEC];
+#pragma unroll
+      for (int t = 0; t < SM; ++t)
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+          float a = 0.f;
+          if (t < S) {
+#pragma unroll
+            for (int s = 0; s < SM; ++s)
+              if (s < S) a = fmaf(c_mix[s * S + t], xs[s][v], a);
+            a = fmaf(c_out[t], yv[v], a);
+          }
+          nx[t][v] = a;
+        }
+#pragma unroll
+      for (int t = 0; t < SM; ++t) {
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) xs[t][v] = nx[t][v];
+        if (t < S && !src_rows) {
+          if constexpr (VEC == 4) *reinterpret_cast<float4*>(xr + (size_t)t * D + d) = make_float4(nx[t][0], nx[t][1], nx[t][2], nx[t][3]);
+          else xr[(size_t)t * D + d] = nx[t][0];
+        }
+      }
+    }
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      float u = 0.f;
+#pragma unroll
+      for (int s = 0; s < SM; ++s)
+        if (s < S) u = fmaf(c_in[s], xs[s][v], u);
+      hc_row[d + v] = u;
+      ss = fmaf(u, u, ss);
+    }
   }
   if (!out_f32 && !out_t) return;
   float r = 1.0f;
   if (g) r = 1.0f / sqrtf(block_sum(ss, red) / (float)D + eps) * ldf(g);
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {       // every thread reads back what it wrote
-    const float v = hc_row[d] * r;
-    if (out_f32) out_f32[(size_t)m * D + d] = v;
-    if (out_t) stf(out_t + (size_t)m * D + d, v);
+  for (int d = threadIdx.x * VEC; d < D; d += blockDim.x * VEC) {   // every thread reads back what it wrote
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      const float o = hc_row[d + v] * r;
+      if (out_f32) out_f32[(size_t)m * D + d + v] = o;
+      if (out_t) stf(out_t + (size_t)m * D + d + v, o);
+    }
   }
 }
 

@@ -214,7 +214,7 @@ __device__ __forceinline__ float gqa_gate(const float* gate, int mode, size_t m,
 // ---------------------------------------------------------------------------------------------------------------------------
 // Pooled blocks: when a step appends the last token of block b (tokens b * P .. b * P + P - 1) of a request, the block's pooled row
 // — the mean over its P cached rows, keys and values alike, fp32 sum — is stored at pool_rows + row(slot, b).  grid (requests of the
-// step, blocks a request can complete in it); the threads walk the row's entries.
+// step, blocks a request can complete in it, 128-entry pieces of the row).
 // ---------------------------------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void gqa_pool_blocks_kernel(T* __restrict__ pool, Paging pg, size_t pool_rows, const Item* __restrict__ seqs, int P, int rowlen) {
@@ -223,11 +223,11 @@ __global__ void gqa_pool_blocks_kernel(T* __restrict__ pool, Paging pg, size_t p
   if (b >= (sq.pos0 + sq.n_rows) / P) return;
   T* dst = pool + (pool_rows + pg.row(sq.slot, b)) * (size_t)rowlen;
   const float inv = 1.0f / (float)P;
-  for (int c = threadIdx.x; c < rowlen; c += blockDim.x) {
-    float a = 0.f;
-    for (int t = 0; t < P; ++t) a += ldf(pool + pg.row(sq.slot, b * P + t) * (size_t)rowlen + c);
-    stf(dst + c, a * inv);
-  }
+  const int c = blockIdx.z * blockDim.x + threadIdx.x;
+  if (c >= rowlen) return;
+  float a = 0.f;
+  for (int t = 0; t < P; ++t) a += ldf(pool + pg.row(sq.slot, b * P + t) * (size_t)rowlen + c);
+  stf(dst + c, a * inv);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------------

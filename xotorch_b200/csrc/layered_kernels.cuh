@@ -513,17 +513,17 @@ __global__ void delta_rule_kernel(DeltaSrc ksrc, DeltaSrc rsrc, DeltaSrc vsrc, c
 
 // Output side of the recurrent mixers: per (row, head) o / rms(o) * w_norm * sigmoid(gate) -> T, the operand of the output product.
 // w_head_stride: dv when every head has its own norm weight, 0 when the heads share one of size dv.  gate_silu: 0 = sigmoid(gate),
-// 1 = silu(gate).  in_head_stride: entries a head holds in o_raw (dv, or dv + 1 when the entry after the values is a normaliser
-// n . q: then, with den_floor [M, H], o <- o / (max(|n . q|, den_floor) + 1e-6) before the norm).
+// 1 = silu(gate).  nq != NULL (with den_floor, both [M, H]): the head's read-out is first divided by max(|nq|, den_floor) + 1e-6
+// (a normaliser n . q that must not fall below a floor).
 template <typename T>
-__global__ void head_norm_gate_kernel(const float* __restrict__ o_raw, int in_head_stride, const float* __restrict__ den_floor, const T* __restrict__ w_norm,
-                                      int w_head_stride, const float* __restrict__ gate, int gate_ld, int gate_col0, int gate_silu, T* __restrict__ out, int H,
-                                      int dv, float eps, int M) {
+__global__ void head_norm_gate_kernel(const float* __restrict__ o_raw, const float* __restrict__ nq, const float* __restrict__ den_floor,
+                                      const T* __restrict__ w_norm, int w_head_stride, const float* __restrict__ gate, int gate_ld, int gate_col0, int gate_silu,
+                                      T* __restrict__ out, int H, int dv, float eps, int M) {
   const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (idx >= M * H) return;
   const int m = idx / H, h = idx % H;
-  const float* o = o_raw + (size_t)m * H * in_head_stride + (size_t)h * in_head_stride;
-  const float pre = den_floor ? 1.0f / (fmaxf(fabsf(o[dv]), den_floor[idx]) + 1e-6f) : 1.0f;
+  const float* o = o_raw + (size_t)m * H * dv + (size_t)h * dv;
+  const float pre = nq ? 1.0f / (fmaxf(fabsf(nq[idx]), den_floor[idx]) + 1e-6f) : 1.0f;
   float s = 0.f;
   for (int d = lane; d < dv; d += 32) { const float v = o[d] * pre; s = fmaf(v, v, s); }
   const float rs = pre / sqrtf(warp_sum(s) / (float)dv + eps);
