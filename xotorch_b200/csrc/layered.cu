@@ -5,8 +5,8 @@
 //   loader    : strict safetensors reader (mmap -> device staging -> widen/copy kernel into the blob);
 //   state     : paged cache (one pool per attention layer that owns keys/values or latents, page table per slot, host free list)
 //               + fp32 recurrent states and convolution inputs per slot; slots are emptied and reused, pages return to the pool;
-//   step      : a packed batch of rows through the layers on one stream (kernels in layered_kernels.cuh), logits / argmax of the
-//               wanted rows back to the host.
+//   step      : a packed batch of rows through the layers on one stream (kernels in layered_kernels.cuh; the second mixer of a
+//               two-mixer layer on a side stream beside the first), logits / argmax of the wanted rows back to the host.
 #include <cuda_runtime.h>
 #include <dirent.h>
 #include <fcntl.h>
@@ -125,8 +125,9 @@ struct xotb200_lm {
   int device = 0, sm_count = 148;
   bool first = false, last = false;
   size_t esz = 2;
-  cudaStream_t stream = nullptr;
-  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  cudaStream_t stream = nullptr;                       // the stream every launch goes to (the second mixer of a layer swaps in `side`)
+  cudaStream_t side = nullptr;                         // second mixer of a two-mixer layer: runs beside the first, joined before the layer goes on
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev_fork = nullptr, ev_join = nullptr;
   char* blob = nullptr;
   size_t blob_elems = 0;
   size_t embed = 0, final_norm = 0, head = 0, embed_norm = 0;
@@ -162,6 +163,7 @@ struct xotb200_lm {
   int max_heads_rec = 0;
   bool pre_scalar = false;
   size_t final_norm_b = 0, pos_table = 0;
+  void* oh2 = nullptr;                                 // the second mixer's operand of its output product
   void *h = nullptr, *cqn = nullptr, *qn = nullptr, *olat = nullptr, *oh = nullptr, *act = nullptr, *th = nullptr, *hw = nullptr;
   void *q16 = nullptr, *cbuf = nullptr, *knx = nullptr, *vxx = nullptr;   // expanded prompt attention (bf16)
   size_t flash_keys_cap = 0;
@@ -467,6 +469,7 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
     return 0;
     };
     if (s.par_on) {
+      REQUIRE(pre_scalar, "layer %d: a second mixer in a layer goes with the pre-norm block form with one-number weights", li);
       REQUIRE(s.mixer == XOTB200_LM_MIX_ATTENTION || s.mixer == XOTB200_LM_MIX_GATED_DELTA || s.mixer == XOTB200_LM_MIX_MATRIX_LSTM || s.mixer == XOTB200_LM_MIX_MAMBA2,
               "layer %d: mixer kind %d cannot share a layer", li, s.mixer);
       REQUIRE(s.par_mixer == XOTB200_LM_MIX_GATED_DELTA || s.par_mixer == XOTB200_LM_MIX_MATRIX_LSTM || s.par_mixer == XOTB200_LM_MIX_MAMBA2,
@@ -764,6 +767,7 @@ static int ensure_scratch(xotb200_lm* e, int M, int n_want) {
     if (z == 2) TRY(regrow(e->q16, m * e->max_q * 2));
     TRY(regrow(e->olat, m * e->max_olat * z));
     TRY(regrow(e->oh, m * e->max_oh * z));
+    if (e->pre_scalar) TRY(regrow(e->oh2, m * e->max_oh * z));
     TRY(regrow(e->act, m * e->max_ff * z));
     TRY(regrow(e->th, m * e->max_lr * z));
     e->m_cap = (int)m;
@@ -1131,7 +1135,7 @@ static int filter_channels(xotb200_lm* e, LmLayer& L, const StepPlan& sp, int co
 }
 
 template <typename T>
-static int gated_delta_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp, float* yout) {
+static int gated_delta_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp, float* yout, void* ohbuf) {
   const xotb200_lm_layer& s = L.s;
   const int D = e->cfg.width, M = sp.M, H = s.heads, G = s.kv_heads, dk = s.dim, dv = s.vdim, C = L.conv_ch;
   TRY(filter_channels<T>(e, L, sp, L.c_r, C, nullptr));
@@ -1140,18 +1144,18 @@ static int gated_delta_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp, floa
   CK(cudaGetLastError());
   e->launches++;
   TRY(run_delta(e, L, sp, DeltaSrc{e->dkk, H * dk, 0}, DeltaSrc{e->drr, H * dk, 0}, DeltaSrc{e->cvb, C, 2 * G * dk}, dk, dv, true));
-  head_norm_gate_kernel<T><<<cdiv((long)M * H, 8), 256, 0, e->stream>>>(e->oraw, nullptr, nullptr, at<T>(e, L.onorm), 0, e->proj, L.ld_in, L.c_g, 1, static_cast<T*>(e->oh),
+  head_norm_gate_kernel<T><<<cdiv((long)M * H, 8), 256, 0, e->stream>>>(e->oraw, nullptr, nullptr, at<T>(e, L.onorm), 0, e->proj, L.ld_in, L.c_g, 1, static_cast<T*>(ohbuf),
                                                                        H, dv, e->cfg.norm_eps, M);
   CK(cudaGetLastError());
   e->launches++;
-  TRY((product<T, T, float, 0>(e, static_cast<T*>(e->oh), (long)H * dv, 0, at<T>(e, L.wo), (long)H * dv, 1, 0, yout, D, 0, M, D, H * dv, 1)));
+  TRY((product<T, T, float, 0>(e, static_cast<T*>(ohbuf), (long)H * dv, 0, at<T>(e, L.wo), (long)H * dv, 1, 0, yout, D, 0, M, D, H * dv, 1)));
   return 0;
 }
 
 // matrix LSTM: gates (a scan per request and head), vectors, the normaliser's own small recurrence, the shared recurrence kernel on
 // the [dk, dv] states, normaliser + head norm + sigmoid gate, output product
 template <typename T>
-static int matrix_lstm_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp, float* yout) {
+static int matrix_lstm_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp, float* yout, void* ohbuf) {
   const xotb200_lm_layer& s = L.s;
   const int D = e->cfg.width, M = sp.M, H = s.heads, dk = s.dim, dv = s.vdim;
   mlstm_gates_kernel<T><<<cdiv((long)sp.n_seq * H, 4), 128, 0, e->stream>>>(e->proj, L.ld_in, L.c_i, L.c_f, at<T>(e, L.i_b), at<T>(e, L.f_b), s.gate_cap, sp.seqs, sp.n_seq, H,
@@ -1165,17 +1169,17 @@ static int matrix_lstm_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp, floa
   e->launches += 3;
   TRY(run_delta(e, L, sp, DeltaSrc{e->dkk, H * dk, 0}, DeltaSrc{e->drr, H * dk, 0}, DeltaSrc{e->proj, L.ld_in, L.c_v}, dk, dv, false));
   head_norm_gate_kernel<T><<<cdiv((long)M * H, 8), 256, 0, e->stream>>>(e->oraw, e->gnq, e->gfloor, at<T>(e, L.onorm), dv, e->proj, L.ld_in, L.c_g, 0,
-                                                                       static_cast<T*>(e->oh), H, dv, e->cfg.norm_eps, M);
+                                                                       static_cast<T*>(ohbuf), H, dv, e->cfg.norm_eps, M);
   CK(cudaGetLastError());
   e->launches++;
-  TRY((product<T, T, float, 0>(e, static_cast<T*>(e->oh), (long)H * dv, 0, at<T>(e, L.wo), (long)H * dv, 1, 0, yout, D, 0, M, D, H * dv, 1)));
+  TRY((product<T, T, float, 0>(e, static_cast<T*>(ohbuf), (long)H * dv, 0, at<T>(e, L.wo), (long)H * dv, 1, 0, yout, D, 0, M, D, H * dv, 1)));
   return 0;
 }
 
 // state-space layer: filter + silu on [x | B | C], step sizes and decays, the shared recurrence kernel, skip + gate + grouped norm,
 // output product
 template <typename T>
-static int mamba2_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp, float* yout) {
+static int mamba2_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp, float* yout, void* ohbuf) {
   const xotb200_lm_layer& s = L.s;
   const int D = e->cfg.width, M = sp.M, H = s.heads, G = s.kv_heads, N = s.dim, dv = s.vdim, C = L.conv_ch, inner = H * dv;
   TRY(filter_channels<T>(e, L, sp, L.c_v, C, at<T>(e, L.conv_b)));
@@ -1189,11 +1193,11 @@ static int mamba2_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp, float* yo
     auto ok = mamba2_out_kernel<T>;
     TRY(opt_in_smem(ok, (size_t)part * 4));
     ok<<<M * s.out_norm_groups, std::min(1024, std::max(32, cdiv(part, 4 * 32) * 32)), (size_t)part * 4, e->stream>>>(
-        e->oraw, e->cvb, C, e->proj, L.ld_in, L.c_z, at<T>(e, L.d_skip), at<T>(e, L.onorm), H, dv, s.out_norm_groups, e->cfg.norm_eps, static_cast<T*>(e->oh));
+        e->oraw, e->cvb, C, e->proj, L.ld_in, L.c_z, at<T>(e, L.d_skip), at<T>(e, L.onorm), H, dv, s.out_norm_groups, e->cfg.norm_eps, static_cast<T*>(ohbuf));
   }
   CK(cudaGetLastError());
   e->launches++;
-  TRY((product<T, T, float, 0>(e, static_cast<T*>(e->oh), (long)inner, 0, at<T>(e, L.wo), (long)inner, 1, 0, yout, D, 0, M, D, inner, 1)));
+  TRY((product<T, T, float, 0>(e, static_cast<T*>(ohbuf), (long)inner, 0, at<T>(e, L.wo), (long)inner, 1, 0, yout, D, 0, M, D, inner, 1)));
   return 0;
 }
 
@@ -1303,12 +1307,12 @@ static int feed_forward(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
 }
 
 template <typename T>
-static int run_branch(xotb200_lm* e, LmLayer& L, const StepPlan& sp, float* yout) {
+static int run_branch(xotb200_lm* e, LmLayer& L, const StepPlan& sp, float* yout, void* ohbuf) {
   switch (L.s.mixer) {
     case XOTB200_LM_MIX_ATTENTION: return gqa_layer<T>(e, L, sp, yout);
-    case XOTB200_LM_MIX_GATED_DELTA: return gated_delta_layer<T>(e, L, sp, yout);
-    case XOTB200_LM_MIX_MATRIX_LSTM: return matrix_lstm_layer<T>(e, L, sp, yout);
-    default: return mamba2_layer<T>(e, L, sp, yout);
+    case XOTB200_LM_MIX_GATED_DELTA: return gated_delta_layer<T>(e, L, sp, yout, ohbuf);
+    case XOTB200_LM_MIX_MATRIX_LSTM: return matrix_lstm_layer<T>(e, L, sp, yout, ohbuf);
+    default: return mamba2_layer<T>(e, L, sp, yout, ohbuf);
   }
 }
 
@@ -1318,8 +1322,22 @@ static int run_mixer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
   if (L.s.mixer == XOTB200_LM_MIX_LATENT_ATTN) return attention_layer<T>(e, L, sp);
   if (L.s.mixer == XOTB200_LM_MIX_DELTA_RULE) return delta_layer<T>(e, L, sp);
   TRY((product<T, T, float, 0>(e, static_cast<T*>(e->h), e->cfg.width, 0, at<T>(e, L.w_in), e->cfg.width, 1, 0, e->proj, L.ld_in, 0, sp.M, L.ld_in, e->cfg.width, 1)));
-  TRY(run_branch<T>(e, L, sp, e->y));
-  if (!L.par.empty()) TRY(run_branch<T>(e, L.par[0], sp, e->y2));
+  if (L.par.empty()) return run_branch<T>(e, L, sp, e->y, e->oh);
+  // Two mixers: they share the projection and nothing else (each has its scratch, its state, its operand buffer), so the second runs
+  // on the side stream beside the first — a recurrence walks the tokens with few CTAs, the attention fills the rest of the GPU — and
+  // the layer goes on when both are done.  Inside a captured decode step the two streams become two branches of the graph.
+  CK(cudaEventRecord(e->ev_fork, e->stream));
+  CK(cudaStreamWaitEvent(e->side, e->ev_fork, 0));
+  cudaStream_t main_stream = e->stream;
+  e->stream = e->side;
+  int rc = run_branch<T>(e, L.par[0], sp, e->y2, e->oh2);
+  e->stream = main_stream;
+  if (rc == 0) rc = run_branch<T>(e, L, sp, e->y, e->oh);
+  // joined also after a failed launch: a capture must not end with the side stream still forked
+  cudaError_t j1 = cudaEventRecord(e->ev_join, e->side), j2 = cudaStreamWaitEvent(e->stream, e->ev_join, 0);
+  if (rc < 0) return rc;
+  CK(j1);
+  CK(j2);
   return 0;
 }
 
@@ -1580,7 +1598,9 @@ int xotb200_lm_create(const xotb200_lm_cfg* cfg, const xotb200_lm_layer* layers,
   int rc = build_layout(e, layers);
   if (rc < 0) { delete e; return rc; }
   auto fail = [&](int code) { xotb200_lm_destroy(e); return code; };
-  if (cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess || cudaEventCreate(&e->ev0) != cudaSuccess ||
+  if (cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess || cudaStreamCreateWithFlags(&e->side, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaEventCreateWithFlags(&e->ev_fork, cudaEventDisableTiming) != cudaSuccess || cudaEventCreateWithFlags(&e->ev_join, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreate(&e->ev0) != cudaSuccess ||
       cudaEventCreate(&e->ev1) != cudaSuccess || cudaMalloc(&e->blob, e->blob_elems * e->esz) != cudaSuccess) {
     set_err("device allocation of %zu weight bytes failed: %s", e->blob_elems * e->esz, cudaGetErrorString(cudaGetLastError()));
     return fail(XOTB200_ECUDA);
@@ -1676,7 +1696,7 @@ int xotb200_lm_destroy(xotb200_lm* e) {
     if (L.rel_bucket) cudaFree(L.rel_bucket);
     if (L.rel_tab) cudaFree(L.rel_tab);
   }
-  void* ptrs[] = {e->y2, e->h0, e->gdec, e->ginw, e->gfloor, e->gnq, e->pos_freqs, e->dist_tab, e->moe_xg, e->moe_yg, e->moe_plan, e->dkk, e->drr, e->cvb, e->moe_ids, e->moe_wts, e->mact, e->du, e->dau, e->part, e->q16, e->cbuf, e->knx, e->vxx, e->blob, e->d_stage, e->x, e->y, e->proj, e->qraw, e->qfull, e->wlog, e->oraw, e->logits, e->h, e->cqn, e->qn, e->olat, e->oh, e->act,
+  void* ptrs[] = {e->oh2, e->y2, e->h0, e->gdec, e->ginw, e->gfloor, e->gnq, e->pos_freqs, e->dist_tab, e->moe_xg, e->moe_yg, e->moe_plan, e->dkk, e->drr, e->cvb, e->moe_ids, e->moe_wts, e->mact, e->du, e->dau, e->part, e->q16, e->cbuf, e->knx, e->vxx, e->blob, e->d_stage, e->x, e->y, e->proj, e->qraw, e->qfull, e->wlog, e->oraw, e->logits, e->h, e->cqn, e->qn, e->olat, e->oh, e->act,
                   e->th, e->hw, e->d_argmax, e->trace_buf};
   for (void* p : ptrs)
     if (p) cudaFree(p);
@@ -1686,6 +1706,9 @@ int xotb200_lm_destroy(xotb200_lm* e) {
   if (e->d_err) cudaFree(e->d_err);
   if (e->ev0) cudaEventDestroy(e->ev0);
   if (e->ev1) cudaEventDestroy(e->ev1);
+  if (e->ev_fork) cudaEventDestroy(e->ev_fork);
+  if (e->ev_join) cudaEventDestroy(e->ev_join);
+  if (e->side) cudaStreamDestroy(e->side);
   if (e->stream) cudaStreamDestroy(e->stream);
   delete e;
   return 0;

@@ -2,6 +2,8 @@
 // reads the residual stream itself; a layer norm with weight and bias, or an RMS norm with a weight stored around zero, closes it),
 // with a learned position table or a computed sine/cosine position vector, short causal convolutions in front of a gated delta
 // rule, the two-sided xIELU activation and mixtures of experts (gated silu or relu^2 experts, two routing rules).
+// Also the pre-norm block form whose norm weights are one number each: the stream kept in several copies mixed by
+// hyper-connections, and a causal convolution added to every sublayer input (embed_streams_kernel, hc_open_kernel, short_conv_kernel).
 //
 // Number formats as in layered_kernels.cuh: T is the storage type of weights and GEMM inputs (bf16 serving, float in the 32-bit
 // mode); the residual stream, norms, router, decays, step sizes, unit vectors and every state are fp32 whatever T is.
