@@ -160,16 +160,38 @@ __global__ void short_conv_kernel(const float* __restrict__ proj, int ld, int co
   const float b = bias ? ldf(bias + c) : 0.f;
   const int per = max((sq.n_rows + (int)gridDim.z - 1) / (int)gridDim.z, taps - 1);
   const int t_begin = blockIdx.z * per, t_end = min(sq.n_rows, t_begin + per);
-  for (int t = t_begin; t < t_end; ++t) {
-    float acc = b;
-    for (int i = 0; i < taps; ++i) {
-      const int back = taps - 1 - i, src = t - back;           // row of this step, or (negative) before it
-      const float v = src >= 0 ? proj[(size_t)(sq.row0 + src) * ld + col0 + c] : st[(size_t)(src + taps - 1) * C + c];
-      acc = fmaf(ldf(w + (size_t)c * taps + i), v, acc);
+  // in(p, c) for a row offset src of this step (negative: before it)
+  auto input = [&](int src) { return src >= 0 ? proj[(size_t)(sq.row0 + src) * ld + col0 + c] : st[(size_t)(src + taps - 1) * C + c]; };
+  constexpr int RT = 8;                                        // up to RT taps: weights and the sliding window stay in registers, one load per row
+  if (taps <= RT) {
+    float wr[RT], win[RT];
+#pragma unroll
+    for (int i = 0; i < RT; ++i) {
+      wr[i] = i < taps ? ldf(w + (size_t)c * taps + i) : 0.f;
+      win[i] = (i < taps - 1 && t_begin < t_end) ? input(t_begin - (taps - 1) + i) : 0.f;
     }
-    if (act == 1) acc = siluf_(acc);
-    if (residual) acc += proj[(size_t)(sq.row0 + t) * ld + col0 + c];
-    stf(out + (size_t)(sq.row0 + t) * ld_out + c, acc);
+    for (int t = t_begin; t < t_end; ++t) {
+      const float cur = proj[(size_t)(sq.row0 + t) * ld + col0 + c];
+      float acc = b;
+#pragma unroll
+      for (int i = 0; i < RT; ++i) {
+        if (i == taps - 1) win[i] = cur;
+        if (i < taps) acc = fmaf(wr[i], win[i], acc);
+      }
+#pragma unroll
+      for (int i = 0; i + 1 < RT; ++i) win[i] = win[i + 1];
+      if (act == 1) acc = siluf_(acc);
+      if (residual) acc += cur;
+      stf(out + (size_t)(sq.row0 + t) * ld_out + c, acc);
+    }
+  } else {
+    for (int t = t_begin; t < t_end; ++t) {
+      float acc = b;
+      for (int i = 0; i < taps; ++i) acc = fmaf(ldf(w + (size_t)c * taps + i), input(t - (taps - 1 - i)), acc);
+      if (act == 1) acc = siluf_(acc);
+      if (residual) acc += proj[(size_t)(sq.row0 + t) * ld + col0 + c];
+      stf(out + (size_t)(sq.row0 + t) * ld_out + c, acc);
+    }
   }
   if (blockIdx.z == 0)
     for (int i = 0; i < taps - 1; ++i) {                       // increasing i: entry i + n_rows is still the old one when it is read

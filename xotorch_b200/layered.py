@@ -271,6 +271,8 @@ def _fubelorn_attention(i: int, kind: str, m: dict) -> dict:
   out = dict(mixer=_lib.LM_MIX_ATTENTION, heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=int(m["dim"]), vdim=int(m["vdim"]),
              scale=float(m["scale"]), window=int(mask.get("size", 0)), keep_first=int(mask.get("keep_first", 0)), pool=int(mask.get("pool", 0)),
              **FUBELORN_LEFT[kind])
+  if out["window"] == 0:                                # no window: every earlier token is seen as itself, nothing to keep or pool
+    out.update(keep_first=0, pool=0)
   if rot:
     out.update(rot_dims=int(rot["dims"]), rot_base=float(rot["base"]), rot_layout=_lib.LM_ROT_HALF)
     sc = rot.get("scaling")
