@@ -40,6 +40,7 @@ SINGLE = {
   "window_beyond_the_prompt": ([parallel(left_keep(size=500, keep=2))], {}),
   "attention_odd_sizes": ([parallel(left_keep(heads=3, kv_heads=3, dim=5, vdim=3), right_delta(3, 1, 5, 7, 4))], {"width": 36}),
   "attention_wide_values": ([parallel(left_keep(heads=2, kv_heads=1, dim=40, vdim=72))], {}),
+  "attention_very_wide_values": ([parallel_2(left_pool(heads=2, kv_heads=2, dim=24, vdim=328, rot_dims=12))], {}),
   "delta_one_tap": ([parallel(right=right_delta(2, 2, 8, 8, 1))], {}),
   "delta_seven_taps": ([parallel(right=right_delta(4, 1, 4, 12, 7))], {}),
   "pooled_attention_and_lstm": ([parallel_2()], {}),

@@ -318,7 +318,7 @@ static int build_layout(xotb200_lm* e, const xotb200_lm_layer* all) {
       const int H = s.heads, G = s.kv_heads, dk = s.dim, dv = s.vdim;
       const bool own = s.kv_from < 0;
       REQUIRE(G >= 1 && H % G == 0, "layer %d: %d query heads do not divide into %d key/value heads", li, H, G);
-      REQUIRE(dv >= 1 && dv <= 256 && dk <= 1024, "layer %d: attention sizes dim %d (<= 1024) / vdim %d (1..256)", li, dk, dv);
+      REQUIRE(dv >= 1 && dv <= 512 && dk <= 1024, "layer %d: attention sizes dim %d (<= 1024) / vdim %d (1..512)", li, dk, dv);
       REQUIRE(s.window >= 0 && s.chunk >= 0 && s.softcap >= 0.f, "layer %d: negative window, chunk or softcap", li);
       REQUIRE(s.out_gate >= 0 && s.out_gate <= 2, "layer %d: unknown output gate %d", li, s.out_gate);
       REQUIRE(s.qk_norm >= XOTB200_LM_QKNORM_NONE && s.qk_norm <= XOTB200_LM_QKNORM_HEAD_PLAIN, "layer %d: unknown query/key norm %d", li, s.qk_norm);
@@ -1000,11 +1000,13 @@ static int delta_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp) {
 
 // rows of one request that share a CTA of the warp-per-(row, head) attention kernel: about 32 (row, head) pairs
 static int gqa_rows_per_item(const xotb200_lm_layer& s) { return std::max(1, 32 / (s.heads / s.kv_heads)); }
+// warps of its CTA (one per (row, head) pair): the widest accumulator variant (values above 256) needs too many registers for 32
+static int gqa_item_warps(const xotb200_lm_layer& s, int pairs) { return std::min(s.vdim > 256 ? 16 : 32, pairs); }
 
 // Few CTAs (decoding): the keys of an item are cut into runs so that the GPU is filled; each run at least one 32-key tile.
 // Returns the number of runs and their length.
 static int gqa_key_runs(const xotb200_lm* e, const xotb200_lm_layer& s, int n_items, int max_len, int* run) {
-  const int rep = s.heads / s.kv_heads, qpi = gqa_rows_per_item(s), pairs = qpi * rep, nw = std::min(32, pairs), ytiles = cdiv(pairs, nw);
+  const int rep = s.heads / s.kv_heads, qpi = gqa_rows_per_item(s), pairs = qpi * rep, nw = gqa_item_warps(s, pairs), ytiles = cdiv(pairs, nw);
   int span = std::max(1, max_len);
   if (s.window > 0) span = std::min(span, s.window + qpi);
   if (s.chunk > 0) span = std::min(span, s.chunk + qpi - 1);   // an item's rows may straddle two blocks: its keys start at the first row's block
@@ -1058,7 +1060,7 @@ static int gqa_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp, float* yout)
   const int qpi = gqa_rows_per_item(s);
   const auto& it = sp.items.at(-qpi);   // the lists of this mixer have negative keys
   if (it.second > 0) {
-    const int pairs = qpi * rep, nw = std::min(32, pairs), ytiles = cdiv(pairs, nw);
+    const int pairs = qpi * rep, nw = gqa_item_warps(s, pairs), ytiles = cdiv(pairs, nw);
     const size_t smem = ((size_t)32 * ((dk + dv) | 1) + (size_t)nw * dk) * 4;
     int run = 0;
     const int splits = gqa_key_runs(e, s, it.second, sp.max_len, &run);
@@ -1074,7 +1076,8 @@ static int gqa_layer(xotb200_lm* e, LmLayer& L, const StepPlan& sp, float* yout)
     if (dv <= 32) LAUNCH_GQA(1);
     else if (dv <= 64) LAUNCH_GQA(2);
     else if (dv <= 128) LAUNCH_GQA(4);
-    else LAUNCH_GQA(8);
+    else if (dv <= 256) LAUNCH_GQA(8);
+    else LAUNCH_GQA(16);
 #undef LAUNCH_GQA
     CK(cudaGetLastError());
     e->launches++;
