@@ -115,6 +115,40 @@ def test_long_decoding(dtype):
   n.close()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_prompt_then_decoding_in_a_batch_of_unequal_requests(dtype):
+  """a mid-sized model (blocks of 10 that do not divide the 64-token pages, windows of 70 and 90, 5 kept tokens, partial rotation, grouped
+  state-space layer first) on 650 / 300 / 41 tokens: each prompt whole in one batch, then 30 tokens decoded together, the short request
+  ending early — far keys, many pooled blocks, key runs over several CTAs, states carried over hundreds of tokens"""
+  cfg = config([mamba2(heads=6, vdim=16, state=24, groups=2, norm_groups=3, conv=4, ff=96),
+                parallel_2(left_pool(heads=6, kv_heads=2, dim=32, vdim=40, size=70, pool=10, rot_dims=16, base=5000.0, scaling=(4.0, 1.0, 4.0, 256)),
+                           right_lstm(3, 24, 32, cap=10.0), ff=96),
+                parallel(left_keep(heads=3, kv_heads=3, dim=24, vdim=24, size=90, keep=5), right_delta(6, 3, 16, 24, 4), ff=0),
+                parallel_2(left_pool(heads=4, kv_heads=1, dim=16, vdim=56, size=33, pool=7, rot_dims=16, scaling=None), right_lstm(2, 32, 16), ff=64)],
+               width=120, vocab=300, streams=4, taps=4, mult=0.6)
+  W = random_weights(cfg, 77)
+  lens, extra = [650, 300, 41], 30
+  seqs = [rand_tokens(cfg["vocab"], L + extra, 90 + i) for i, L in enumerate(lens)]
+  refs = [oracle_logits(cfg, W, s)[0] for s in seqs]
+  n = make_engine(cfg, W, dtype, max_tokens=1200, max_requests=3, page_size=64)
+  want = [0, 1, 64, 500, 649, 650 + 0, 650 + 128, 650 + 299, 950 + 40]
+  lg, _ = n.step([0, 1, 2], [s[:L] for s, L in zip(seqs, lens)], want=want)
+  ref = np.stack([refs[0][0], refs[0][1], refs[0][64], refs[0][500], refs[0][649], refs[1][0], refs[1][128], refs[1][299], refs[2][40]])
+  assert rows_agree(lg, ref, dtype), "prompts"
+  live, dec = [0, 1, 2], {0: [], 1: [], 2: []}
+  for t in range(extra):
+    if t == 12:
+      live.remove(2)
+      n.clear_request(2)
+    lg, _ = n.step(live, [seqs[i][lens[i] + t:lens[i] + t + 1] for i in live])
+    for k, i in enumerate(live):
+      dec[i].append(lg[k])
+  for i in range(3):
+    got = np.stack(dec[i])
+    assert rows_agree(got, refs[i][lens[i]:lens[i] + len(got)], dtype), f"decoded tokens of request {i}"
+  n.close()
+
+
 def test_first_tokens_of_a_sequence():
   cfg = config(MIXED)
   W = random_weights(cfg, 9)
