@@ -65,6 +65,7 @@ SINGLE = {
   "input_convolution_of_one_tap": ([parallel(), mamba2()], {"taps": 1}),
   "input_convolution_of_six_taps": ([parallel_2(), mamba2()], {"taps": 6}),
   "unit_multiplier_and_scales": ([parallel(ls=1.0, rs=1.0)], {"mult": 1.0}),
+  "width_not_a_multiple_of_four": ([parallel(), parallel_2(), mamba2()], {"width": 30, "streams": 2}),
 }
 
 
